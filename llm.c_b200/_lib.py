@@ -1,0 +1,96 @@
+"""ctypes bindings of the two native libraries (see build.py).
+
+``cuda()`` returns the kernel library and raises if it is missing on a machine that has a GPU:
+there is no silent PyTorch fallback for device tensors.  ``host()`` returns the host runtime.
+"""
+import ctypes
+import os
+from ctypes import POINTER, Structure, c_float, c_int, c_longlong, c_uint, c_void_p
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIBDIR = os.path.join(HERE, "lib")
+
+_cuda = None
+_host = None
+
+
+class TensorView(Structure):
+    _fields_ = [("p_base", c_longlong), ("p_stride", c_longlong), ("o_base", c_longlong), ("o_stride", c_longlong),
+                ("n", c_longlong), ("L", c_int), ("wd", c_float), ("seed", c_uint), ("pad", c_int)]
+
+
+class TensorTable(Structure):
+    _fields_ = [("t", TensorView * 16), ("count", c_int)]
+
+
+def _load(name, builder):
+    path = os.path.join(LIBDIR, name)
+    if not os.path.exists(path):
+        from . import build as _b
+        getattr(_b, builder)()
+    return ctypes.CDLL(path)
+
+
+def cuda():
+    global _cuda
+    if _cuda is not None:
+        return _cuda
+    lib = _load("libllmc_b200.so", "build_cuda")
+    P, I, L, F, U, S = c_void_p, c_int, c_longlong, c_float, c_uint, c_void_p
+    sigs = {
+        "llmc_status_read": (I, [I, POINTER(c_uint)]),
+        "llmc_tensormap_cache_clear": (None, []),
+        "llmc_device_sm_count": (I, []),
+        "llmc_gemm": (I, [P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, P, I, S]),
+        "llmc_gemm_workspace": (None, [I, I, I, POINTER(c_longlong), POINTER(c_int)]),
+        "llmc_gemm_pick_splits": (I, [I, I, I, I]),
+        "llmc_layernorm_fwd": (I, [P, P, P, P, P, P, I, I, S]),
+        "llmc_fused_residual_fwd": (I, [P, P, P, P, P, P, P, P, I, I, S]),
+        "llmc_layernorm_bwd_scratch": (L, [I, I]),
+        "llmc_layernorm_bwd": (I, [P, P, P, P, P, P, P, P, P, I, I, I, I, S]),
+        "llmc_encoder_fwd": (I, [P, P, P, P, I, I, I, S]),
+        "llmc_encoder_bwd": (I, [P, P, P, P, I, I, I, I, I, I, U, S]),
+        "llmc_fused_classifier": (I, [P, P, P, F, I, I, I, I, I, S]),
+        "llmc_gelu_fwd": (I, [P, P, L, S]),
+        "llmc_gelu_bwd_inplace": (I, [P, P, L, S]),
+        "llmc_residual_add": (I, [P, P, P, L, S]),
+        "llmc_bias_grad_scratch": (L, [I, I]),
+        "llmc_bias_grad": (I, [P, P, P, I, I, I, S]),
+        "llmc_norm_sq_scratch": (I, []),
+        "llmc_global_norm_sq": (I, [P, P, P, POINTER(TensorTable), S]),
+        "llmc_adamw": (I, [P, P, P, P, P, POINTER(TensorTable), F, F, F, F, I, F, P, F, S]),
+        "llmc_params_from_master": (I, [P, P, POINTER(TensorTable), S]),
+        "llmc_master_from_params": (I, [P, P, POINTER(TensorTable), S]),
+        "llmc_attention_fwd": (I, [P, P, P, I, I, I, I, S]),
+        "llmc_attention_bwd": (I, [P, P, P, P, P, P, I, I, I, I, S]),
+    }
+    for name, (res, args) in sigs.items():
+        if hasattr(lib, name):
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+    _cuda = lib
+    return lib
+
+
+def host():
+    global _host
+    if _host is None:
+        _host = _load("libllmc_host.so", "build_host")
+    return _host
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def check(rc, what):
+    if rc != 0:
+        raise KernelError("%s failed with code %d" % (what, rc))
+
+
+def read_status(clear=True):
+    """Synchronises the device and returns the status word (0 = no kernel reported an error)."""
+    out = c_uint(0)
+    check(cuda().llmc_status_read(1 if clear else 0, ctypes.byref(out)), "llmc_status_read")
+    return out.value

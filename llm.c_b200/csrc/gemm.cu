@@ -1,0 +1,507 @@
+// bf16 GEMM family for sm_100a: D[M,N] = A[M,K] * B[N,K]^T with fp32 accumulation in TMEM.
+//
+// One persistent, warp-specialised kernel template covers the three operand layouts a
+// transformer needs and their fused epilogues:
+//   forward   out = inp * W^T (+ bias) (+ GELU, also emitting the pre-activation)      A K-major,  B K-major
+//   dgrad     dinp = dout * W          (* GELU'(pre-activation))                        A K-major,  B MN-major
+//   wgrad     dW (+)= dout^T * inp     (split-K, fixed-order reduction, bf16 accumulate) A MN-major, B MN-major
+// It replaces the cuBLASLt calls of the reference (llmc/matmul.cuh:109-228 and its epilogues
+// BIAS / GELU_AUX_BIAS / DGELU, beta=1 accumulation) with hand-written tcgen05 code.
+//
+// Structure of a CTA (192 threads, one CTA per SM, tiles taken round-robin):
+//   warp 0      TMA producer: fills a 4-stage ring of 128x64 (A) and 256x64 (B) bf16 tiles,
+//               128-byte swizzled, signalling `full[stage]` through complete_tx.
+//   warp 1      MMA issuer: one thread issues tcgen05.mma 128x256x16 four times per stage into one
+//               of two 256-column TMEM accumulators and commits to `empty[stage]`; after the last
+//               k-block it commits to `acc_full[buf]`.
+//   warps 2..5  epilogue: tcgen05.ld the accumulator (each warp owns 32 TMEM lanes = 32 rows), apply
+//               the epilogue, stage bf16 through swizzled shared memory and write with TMA stores,
+//               then release the accumulator (`acc_empty[buf]`) so the next tile's MMAs overlap.
+// No TMA load uses cluster multicast. All waits are bounded (see common.cuh).
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
+constexpr int UMMA_K = 16;
+constexpr int A_STAGE_BYTES = BM * BK * 2;            // 16 KB
+constexpr int B_STAGE_BYTES = BN * BK * 2;            // 32 KB
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int EPI_COLS = 64;                          // columns per epilogue chunk (128 B of bf16)
+constexpr int EPI_BUF_BYTES = BM * EPI_COLS * 2;      // 16 KB
+constexpr int NUM_EPI_BUFS = 2;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + NUM_EPI_BUFS * EPI_BUF_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr int RASTER_GROUP = 16;
+
+enum EpiMode : int {
+    EPI_STORE = 0,      // D = acc (+ bias[n])
+    EPI_GELU = 1,       // aux = acc + bias ; D = gelu(aux)
+    EPI_DGELU = 2,      // D = acc * gelu'(aux)
+    EPI_ACCUM = 3,      // D (+)= acc, optional split-K through a fp32 workspace
+};
+
+struct GemmArgs {
+    int M, N, K;
+    int num_m_tiles, num_n_tiles, splits, kb_per_split, num_kb;
+    bf16* D;            // row-major M x N, leading dimension ldd (elements)
+    int ldd;
+    const bf16* bias;   // N entries or null
+    bf16* aux;          // M x N (ldd) pre-activation: written by EPI_GELU, read by EPI_DGELU
+    float* workspace;   // split-K partials: [tile][split][BM*BN] fp32
+    unsigned int* counters;   // one per tile, zero before the launch, left zero after it
+    int accumulate;     // EPI_ACCUM: add to the existing D
+    unsigned int* status;
+};
+
+DEVINL void epi_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+// barrier over the 128 epilogue threads that also ORs a predicate: every thread gets the same answer
+DEVINL bool epi_any(int pred) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.u32 q, %1, 0;\n\t"
+        "bar.red.or.pred p, 1, 128, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}" : "=r"(r) : "r"(pred) : "memory");
+    return r != 0;
+}
+
+template <int A_MN, int B_MN, int MODE>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+            const __grid_constant__ CUtensorMap tmD, const __grid_constant__ CUtensorMap tmAux, const GemmArgs g) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* epi_smem = smem + STAGES * STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(epi_smem + NUM_EPI_BUFS * EPI_BUF_BYTES);
+    uint64_t* full = bars;                    // [STAGES]
+    uint64_t* empty = bars + STAGES;          // [STAGES]
+    uint64_t* acc_full = bars + 2 * STAGES;   // [2]
+    uint64_t* acc_empty = acc_full + 2;       // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    int* last_flag = const_cast<int*>(abort_flag) + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int total_work = g.num_m_tiles * g.num_n_tiles * g.splits;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int b = 0; b < 2; b++) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 0 && lane == 0) {
+        tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB);
+        if (MODE != EPI_ACCUM) tma_prefetch_desc(&tmD);
+        if (MODE == EPI_GELU) tma_prefetch_desc(&tmAux);
+    }
+    if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    // work item -> (m tile, n tile, split); m tiles are visited in groups so that concurrently
+    // running CTAs share both A and B tiles in L2
+    auto decode = [&](int w, int& mt, int& nt, int& sp) {
+        sp = w % g.splits;
+        int t = w / g.splits;
+        int per_group = RASTER_GROUP * g.num_n_tiles;
+        int grp = t / per_group, within = t - grp * per_group;
+        int gh = min(RASTER_GROUP, g.num_m_tiles - grp * RASTER_GROUP);
+        nt = within / gh;
+        mt = grp * RASTER_GROUP + within - nt * gh;
+    };
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            int stage = 0; uint32_t phase = 0;
+            for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
+                int mt, nt, sp; decode(w, mt, nt, sp);
+                const int kb0 = sp * g.kb_per_split, kb1 = min(g.num_kb, kb0 + g.kb_per_split);
+                for (int kb = kb0; kb < kb1; kb++) {
+                    if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, g.status, 0x100 + stage)) break;
+                    uint8_t* sa = smem + stage * STAGE_BYTES;
+                    uint8_t* sb = sa + A_STAGE_BYTES;
+                    mbar_expect_tx(&full[stage], STAGE_BYTES);
+                    if (A_MN == 0) {
+                        tma_load_2d(sa, &tmA, &full[stage], kb * BK, mt * BM);           // box {64 k, 128 rows}
+                    } else {
+                        #pragma unroll
+                        for (int i = 0; i < BM / 64; i++)                                   // boxes {64 m, 64 k}
+                            tma_load_2d(sa + i * (BK * 128), &tmA, &full[stage], mt * BM + i * 64, kb * BK);
+                    }
+                    if (B_MN == 0) {
+                        tma_load_2d(sb, &tmB, &full[stage], kb * BK, nt * BN);           // box {64 k, 256 rows}
+                    } else {
+                        #pragma unroll
+                        for (int i = 0; i < BN / 64; i++)                                   // boxes {64 n, 64 k}
+                            tma_load_2d(sb + i * (BK * 128), &tmB, &full[stage], nt * BN + i * 64, kb * BK);
+                    }
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (*abort_flag) break;
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN, B_MN);
+            int stage = 0; uint32_t phase = 0;
+            int it = 0;
+            for (int w = blockIdx.x; w < total_work; w += gridDim.x, it++) {
+                int mt, nt, sp; decode(w, mt, nt, sp);
+                const int kb0 = sp * g.kb_per_split, kb1 = min(g.num_kb, kb0 + g.kb_per_split);
+                const int buf = it & 1;
+                const uint32_t use = (uint32_t)(it >> 1);
+                if (!mbar_wait(&acc_empty[buf], (use & 1) ^ 1, abort_flag, g.status, 0x200 + buf)) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int kb = kb0; kb < kb1; kb++) {
+                    if (!mbar_wait(&full[stage], phase, abort_flag, g.status, 0x300 + stage)) break;
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+                    const uint32_t sb = sa + A_STAGE_BYTES;
+                    #pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; k++) {
+                        uint64_t da, db;
+                        if (A_MN == 0) da = umma_desc_sw128(sa + k * (UMMA_K * 2), 16, 1024);
+                        else           da = umma_desc_sw128(sa + k * (UMMA_K * 128), BK * 128, 1024);
+                        if (B_MN == 0) db = umma_desc_sw128(sb + k * (UMMA_K * 2), 16, 1024);
+                        else           db = umma_desc_sw128(sb + k * (UMMA_K * 128), BK * 128, 1024);
+                        umma_ss(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&empty[stage]);      // frees the smem stage once these MMAs have read it
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                umma_commit(&acc_full[buf]);          // accumulator complete
+                if (*abort_flag) break;
+            }
+        }
+    } else {
+        // ---------------- epilogue (warps 2..5) ----------------
+        const int q = warp & 3;                        // TMEM lane quarter this warp may access
+        const int row = q * 32 + lane;                 // row of the tile owned by this thread
+        const bool store_thread = (threadIdx.x == 64);
+        int it = 0;
+        uint32_t chunk_ctr = 0;
+        for (int w = blockIdx.x; w < total_work; w += gridDim.x, it++) {
+            int mt, nt, sp; decode(w, mt, nt, sp);
+            const int buf = it & 1;
+            const uint32_t use = (uint32_t)(it >> 1);
+            const bool ok = mbar_wait(&acc_full[buf], use & 1, abort_flag, g.status, 0x400 + buf);
+            tc_fence_after();
+            const int m0 = mt * BM, n0 = nt * BN;
+            const int grow = m0 + row;
+            const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
+
+            if (MODE != EPI_ACCUM) {
+                #pragma unroll 1
+                for (int c = 0; c < BN / EPI_COLS; c++) {
+                    const int col0 = n0 + c * EPI_COLS;
+                    if (col0 >= g.N) break;           // uniform over the CTA
+                    uint32_t v[64];
+                    tmem_ld32(t_row + c * EPI_COLS, v);
+                    tmem_ld32(t_row + c * EPI_COLS + 32, v + 32);
+                    tmem_ld_wait();
+                    float* f = reinterpret_cast<float*>(v);
+                    if (MODE == EPI_STORE || MODE == EPI_GELU) {
+                        if (g.bias != nullptr) {
+                            #pragma unroll
+                            for (int j = 0; j < 64; j += 8) {
+                                if (col0 + j < g.N) {   // N is a multiple of 8
+                                    bf16x8 b = ld128(g.bias + col0 + j);
+                                    #pragma unroll
+                                    for (int e = 0; e < 8; e++) f[j + e] += __bfloat162float(b[e]);
+                                }
+                            }
+                        }
+                    }
+                    uint8_t* sbuf0; uint8_t* sbuf1 = nullptr;
+                    if (MODE == EPI_GELU) {
+                        // both staging buffers are used by this chunk: wait for every earlier store to have read them
+                        if (store_thread) tma_store_wait_read<0>();
+                        sbuf0 = epi_smem; sbuf1 = epi_smem + EPI_BUF_BYTES;
+                    } else {
+                        if (store_thread) tma_store_wait_read<1>();
+                        sbuf0 = epi_smem + (chunk_ctr & 1) * EPI_BUF_BYTES;
+                    }
+                    chunk_ctr++;
+                    epi_barrier();
+                    if (MODE == EPI_DGELU) {
+                        const bool rok = grow < g.M;
+                        #pragma unroll
+                        for (int j = 0; j < 64; j += 8) {
+                            if (rok && col0 + j < g.N) {
+                                bf16x8 a = ld128cs(g.aux + (size_t)grow * g.ldd + col0 + j);
+                                #pragma unroll
+                                for (int e = 0; e < 8; e++) f[j + e] *= gelu_tanh_grad(__bfloat162float(a[e]));
+                            }
+                        }
+                    }
+                    // 128-byte swizzle: 16-byte chunk j of row r lives at chunk position j ^ (r & 7)
+                    uint8_t* srow0 = sbuf0 + row * 128;
+                    if (MODE == EPI_GELU) {
+                        uint8_t* srow1 = sbuf1 + row * 128;
+                        #pragma unroll
+                        for (int j = 0; j < 8; j++) {
+                            uint4 pre, post;
+                            float x0 = f[j*8+0], x1 = f[j*8+1], x2 = f[j*8+2], x3 = f[j*8+3];
+                            float x4 = f[j*8+4], x5 = f[j*8+5], x6 = f[j*8+6], x7 = f[j*8+7];
+                            pre.x = pack_bf16x2(x0, x1); pre.y = pack_bf16x2(x2, x3);
+                            pre.z = pack_bf16x2(x4, x5); pre.w = pack_bf16x2(x6, x7);
+                            // GELU is applied to the bf16-rounded pre-activation so that a later recompute
+                            // from the stored pre-activation reproduces the same values
+                            float2 r0 = unpack_bf16x2(pre.x), r1 = unpack_bf16x2(pre.y), r2 = unpack_bf16x2(pre.z), r3 = unpack_bf16x2(pre.w);
+                            post.x = pack_bf16x2(gelu_tanh(r0.x), gelu_tanh(r0.y));
+                            post.y = pack_bf16x2(gelu_tanh(r1.x), gelu_tanh(r1.y));
+                            post.z = pack_bf16x2(gelu_tanh(r2.x), gelu_tanh(r2.y));
+                            post.w = pack_bf16x2(gelu_tanh(r3.x), gelu_tanh(r3.y));
+                            const int pos = (j ^ (row & 7)) * 16;
+                            *reinterpret_cast<uint4*>(srow1 + pos) = pre;
+                            *reinterpret_cast<uint4*>(srow0 + pos) = post;
+                        }
+                    } else {
+                        #pragma unroll
+                        for (int j = 0; j < 8; j++) {
+                            uint4 o;
+                            o.x = pack_bf16x2(f[j*8+0], f[j*8+1]); o.y = pack_bf16x2(f[j*8+2], f[j*8+3]);
+                            o.z = pack_bf16x2(f[j*8+4], f[j*8+5]); o.w = pack_bf16x2(f[j*8+6], f[j*8+7]);
+                            *reinterpret_cast<uint4*>(srow0 + ((j ^ (row & 7)) * 16)) = o;
+                        }
+                    }
+                    fence_async_smem();
+                    epi_barrier();
+                    if (store_thread && ok) {
+                        tma_store_2d(&tmD, sbuf0, col0, m0);
+                        if (MODE == EPI_GELU) tma_store_2d(&tmAux, sbuf1, col0, m0);
+                        tma_store_commit();
+                    }
+                }
+                // accumulator fully read: hand it back to the MMA warp
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&acc_empty[buf]);
+            } else {
+                // ---- EPI_ACCUM: direct global read-modify-write, optional split-K ----
+                const int tile = mt * g.num_n_tiles + nt;
+                if (g.splits == 1) {
+                    #pragma unroll 1
+                    for (int c = 0; c < BN / 32; c++) {
+                        const int col0 = n0 + c * 32;
+                        if (col0 >= g.N) break;
+                        uint32_t v[32];
+                        tmem_ld32(t_row + c * 32, v);
+                        tmem_ld_wait();
+                        float* f = reinterpret_cast<float*>(v);
+                        if (grow < g.M && ok) {
+                            #pragma unroll
+                            for (int j = 0; j < 32; j += 8) {
+                                if (col0 + j < g.N) {
+                                    bf16* dp = g.D + (size_t)grow * g.ldd + col0 + j;
+                                    bf16x8 o;
+                                    if (g.accumulate) {
+                                        bf16x8 old = ld128(dp);
+                                        #pragma unroll
+                                        for (int e = 0; e < 8; e++) o[e] = __float2bfloat16_rn(f[j + e] + __bfloat162float(old[e]));
+                                    } else {
+                                        #pragma unroll
+                                        for (int e = 0; e < 8; e++) o[e] = __float2bfloat16_rn(f[j + e]);
+                                    }
+                                    st128(dp, o);
+                                }
+                            }
+                        }
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                } else {
+                    // partial tile -> workspace, laid out [col/4][row][4] so that a warp writes 512 contiguous bytes
+                    float* wsp = g.workspace + ((size_t)tile * g.splits + sp) * (BM * BN);
+                    #pragma unroll 1
+                    for (int c = 0; c < BN / 32; c++) {
+                        uint32_t v[32];
+                        tmem_ld32(t_row + c * 32, v);
+                        tmem_ld_wait();
+                        #pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            float4 o = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j+1]), __uint_as_float(v[j+2]), __uint_as_float(v[j+3]));
+                            __stcg(reinterpret_cast<float4*>(wsp + ((size_t)((c * 32 + j) >> 2) * BM + row) * 4), o);
+                        }
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&acc_empty[buf]);
+                    __threadfence();
+                    epi_barrier();
+                    if (store_thread) {
+                        unsigned int prev = atomicAdd(&g.counters[tile], 1u);
+                        *last_flag = (prev == (unsigned int)(g.splits - 1));
+                        if (prev == (unsigned int)(g.splits - 1)) g.counters[tile] = 0;   // ready for the next launch
+                    }
+                    epi_barrier();
+                    if (*last_flag && ok) {
+                        __threadfence();
+                        const float* wt = g.workspace + (size_t)tile * g.splits * (BM * BN);
+                        if (grow < g.M) {
+                            #pragma unroll 1
+                            for (int j = 0; j < BN; j += 8) {
+                                if (n0 + j >= g.N) break;
+                                float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                                for (int s = 0; s < g.splits; s++) {      // fixed order: deterministic
+                                    const float* p = wt + (size_t)s * (BM * BN);
+                                    float4 a = __ldcg(reinterpret_cast<const float4*>(p + ((size_t)(j >> 2) * BM + row) * 4));
+                                    float4 b = __ldcg(reinterpret_cast<const float4*>(p + ((size_t)((j >> 2) + 1) * BM + row) * 4));
+                                    acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+                                    acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+                                }
+                                bf16* dp = g.D + (size_t)grow * g.ldd + n0 + j;
+                                bf16x8 o;
+                                if (g.accumulate) {
+                                    bf16x8 old = ld128(dp);
+                                    #pragma unroll
+                                    for (int e = 0; e < 8; e++) o[e] = __float2bfloat16_rn(acc[e] + __bfloat162float(old[e]));
+                                } else {
+                                    #pragma unroll
+                                    for (int e = 0; e < 8; e++) o[e] = __float2bfloat16_rn(acc[e]);
+                                }
+                                st128(dp, o);
+                            }
+                        }
+                    }
+                    epi_barrier();   // last_flag is rewritten by the next tile
+                }
+            }
+            if (epi_any(*abort_flag)) break;   // uniform decision: nobody is left alone at a barrier
+        }
+        if (store_thread) tma_store_wait<0>();
+    }
+
+    // teardown: everybody meets, then the allocating warp frees TMEM
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (*abort_flag) {
+        // a wait was abandoned: give copies that are still in flight time to land before the CTA's
+        // shared memory is released
+        long long t0 = clock64();
+        while (clock64() - t0 < 2000000ll) { __nanosleep(1000); }
+        __syncthreads();
+    }
+    if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+int make_operand_map(CUtensorMap* tm, const bf16* ptr, int mn_major, int mn_extent, int k_extent, int ld, int tile_mn) {
+    uint64_t dims[2], strides[2]; uint32_t box[2];
+    if (mn_major == 0) {            // stored [mn][k], k contiguous
+        dims[0] = (uint64_t)k_extent; dims[1] = (uint64_t)mn_extent;
+        box[0] = BK; box[1] = (uint32_t)tile_mn;
+    } else {                        // stored [k][mn], mn contiguous
+        dims[0] = (uint64_t)mn_extent; dims[1] = (uint64_t)k_extent;
+        box[0] = 64; box[1] = BK;
+    }
+    strides[0] = 2; strides[1] = (uint64_t)ld * 2;
+    return llmc_get_tensormap(tm, ptr, 2, 2, dims, strides, box, 3);
+}
+
+template <int A_MN, int B_MN, int MODE>
+int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmD, const CUtensorMap& tmAux,
+           const GemmArgs& g, int grid, cudaStream_t stream) {
+    static bool configured = false;
+    auto kfn = gemm_kernel<A_MN, B_MN, MODE>;
+    if (!configured) {
+        CUDA_CHECK(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        configured = true;
+    }
+    kfn<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, tmD, tmAux, g);
+    CUDA_CHECK(cudaGetLastError());
+    return 0;
+}
+
+}  // namespace
+
+// Number of fp32 workspace elements and counters llmc_gemm needs for a given problem
+extern "C" void llmc_gemm_workspace(int M, int N, int splits, long long* ws_floats, int* num_counters) {
+    int tiles = CEIL_DIV(M, BM) * CEIL_DIV(N, BN);
+    *ws_floats = splits > 1 ? (long long)tiles * splits * BM * BN : 0;
+    *num_counters = tiles;
+}
+
+// Pick a split-K factor that fills the machine for a wgrad-shaped problem
+extern "C" int llmc_gemm_pick_splits(int M, int N, int K, int sm_count) {
+    int tiles = CEIL_DIV(M, BM) * CEIL_DIV(N, BN);
+    int num_kb = CEIL_DIV(K, BK);
+    if (tiles >= sm_count || num_kb < 16) return 1;
+    int best = 1; double best_eff = 0.0;
+    for (int s = 1; s <= 32 && s * 8 <= num_kb; s++) {
+        int work = tiles * s;
+        int waves = CEIL_DIV(work, sm_count);
+        double eff = (double)work / ((double)waves * sm_count);
+        // splitting costs a workspace round trip: prefer fewer splits on ties
+        if (eff > best_eff + 0.02) { best_eff = eff; best = s; }
+    }
+    return best;
+}
+
+// D[M,N] = op(A) * op(B)^T with the epilogue selected by `mode` (EpiMode).
+//   a_mn_major = 0: A is stored [M][K] (lda = row stride);  1: stored [K][M]
+//   b_mn_major = 0: B is stored [N][K] (ldb = row stride);  1: stored [K][N]
+// All leading dimensions in elements and multiples of 8; pointers 16-byte aligned.
+extern "C" int llmc_gemm(const bf16* A, const bf16* B, bf16* D, const bf16* bias, bf16* aux,
+                         int M, int N, int K, int lda, int ldb, int ldd,
+                         int a_mn_major, int b_mn_major, int mode, int accumulate,
+                         int splits, float* workspace, unsigned int* counters,
+                         int max_ctas, cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    if ((N % 8) || (lda % 8) || (ldb % 8) || (ldd % 8)) { fprintf(stderr, "[llmc_b200] gemm: N and leading dimensions must be multiples of 8\n"); return -1; }
+    GemmArgs g;
+    g.M = M; g.N = N; g.K = K;
+    g.num_m_tiles = CEIL_DIV(M, BM); g.num_n_tiles = CEIL_DIV(N, BN);
+    g.num_kb = CEIL_DIV(K, BK);
+    if (mode != EPI_ACCUM || splits < 1) splits = 1;
+    if (splits > g.num_kb) splits = g.num_kb;
+    g.kb_per_split = CEIL_DIV(g.num_kb, splits);
+    splits = CEIL_DIV(g.num_kb, g.kb_per_split);      // no empty split
+    g.splits = splits;
+    if (splits > 1 && (workspace == nullptr || counters == nullptr)) { fprintf(stderr, "[llmc_b200] gemm: split-K needs workspace\n"); return -1; }
+    g.D = D; g.ldd = ldd; g.bias = bias; g.aux = aux; g.workspace = workspace; g.counters = counters;
+    g.accumulate = accumulate;
+    g.status = llmc_status_ptr();
+
+    CUtensorMap tmA, tmB, tmD, tmAux;
+    int rc;
+    if ((rc = make_operand_map(&tmA, A, a_mn_major, M, K, lda, BM))) return rc;
+    if ((rc = make_operand_map(&tmB, B, b_mn_major, N, K, ldb, BN))) return rc;
+    {
+        uint64_t dims[2] = {(uint64_t)N, (uint64_t)M}, strides[2] = {2, (uint64_t)ldd * 2};
+        uint32_t box[2] = {EPI_COLS, BM};
+        if ((rc = llmc_get_tensormap(&tmD, D, 2, 2, dims, strides, box, 3))) return rc;
+        tmAux = tmD;
+        if (mode == EPI_GELU) { if ((rc = llmc_get_tensormap(&tmAux, aux, 2, 2, dims, strides, box, 3))) return rc; }
+    }
+    int sms = llmc_device_sm_count();
+    if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
+    int total = g.num_m_tiles * g.num_n_tiles * g.splits;
+    int grid = total < sms ? total : sms;
+    if (grid < 1) grid = 1;
+
+#define LAUNCH(AM, BMj, MD) return launch<AM, BMj, MD>(tmA, tmB, tmD, tmAux, g, grid, stream)
+    if (a_mn_major == 0 && b_mn_major == 0) {
+        if (mode == EPI_STORE) LAUNCH(0, 0, EPI_STORE);
+        if (mode == EPI_GELU) LAUNCH(0, 0, EPI_GELU);
+        if (mode == EPI_ACCUM) LAUNCH(0, 0, EPI_ACCUM);
+    } else if (a_mn_major == 0 && b_mn_major == 1) {
+        if (mode == EPI_STORE) LAUNCH(0, 1, EPI_STORE);
+        if (mode == EPI_DGELU) LAUNCH(0, 1, EPI_DGELU);
+    } else if (a_mn_major == 1 && b_mn_major == 1) {
+        if (mode == EPI_ACCUM) LAUNCH(1, 1, EPI_ACCUM);
+        if (mode == EPI_STORE) LAUNCH(1, 1, EPI_STORE);
+    }
+#undef LAUNCH
+    fprintf(stderr, "[llmc_b200] gemm: unsupported layout/mode combination (%d,%d,%d)\n", a_mn_major, b_mn_major, mode);
+    return -1;
+}

@@ -1,0 +1,227 @@
+// LayerNorm forward, fused residual-add + LayerNorm forward, and LayerNorm backward for bf16
+// activations with fp32 statistics.
+//
+// Forward: one warp per row, 128-bit loads, the row stays in registers between the mean/variance
+// passes and the normalise pass (rows up to 8192 channels; wider rows re-read through L1).
+// Backward: each CTA walks a contiguous strip of rows; every lane keeps the dweight/dbias partial
+// sums of "its" channels in registers across the strip, the CTA folds its warps in a fixed order
+// and writes one fp32 partial row per CTA; a second tiny kernel folds the CTA partials in CTA order
+// and accumulates into the bf16 gradients.  No float atomics anywhere: results are bit-reproducible.
+//
+// Capability parity: llmc/layernorm.cuh (layernorm_forward, fused_residual_forward5,
+// layernorm_backward) of the reference.
+#include "common.cuh"
+
+namespace {
+
+constexpr int MAXP = 4;   // packs (of 8 channels) per lane held in registers => rows up to 32*8*MAXP = 1024 per "slab"
+// Rows wider than a slab are processed slab by slab.
+
+template <bool FUSED_RESIDUAL>
+__global__ void __launch_bounds__(256)
+ln_fwd_kernel(bf16* __restrict__ out, float* __restrict__ mean_out, float* __restrict__ rstd_out,
+              bf16* __restrict__ residual_out, const bf16* __restrict__ inp1, const bf16* __restrict__ inp2,
+              const bf16* __restrict__ weight, const bf16* __restrict__ bias, int N, int C) {
+    const int warps_per_block = blockDim.x >> 5;
+    const int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+    if (row >= N) return;
+    const int lane = threadIdx.x & 31;
+    const int npack = C >> 3;
+    const bf16* x1 = inp1 + (size_t)row * C;
+    const bf16* x2 = FUSED_RESIDUAL ? inp2 + (size_t)row * C : nullptr;
+    bf16* res = FUSED_RESIDUAL ? residual_out + (size_t)row * C : nullptr;
+
+    // pass 1: (residual add,) sum
+    float sum = 0.f;
+    for (int p = lane; p < npack; p += 32) {
+        bf16x8 a = ld128cs(x1 + p * 8);
+        if (FUSED_RESIDUAL) {
+            bf16x8 b = ld128cs(x2 + p * 8);
+            #pragma unroll
+            for (int e = 0; e < 8; e++) a[e] = __float2bfloat16_rn(__bfloat162float(a[e]) + __bfloat162float(b[e]));
+            st128(res + p * 8, a);
+        }
+        #pragma unroll
+        for (int e = 0; e < 8; e++) sum += __bfloat162float(a[e]);
+    }
+    const float mean = warp_sum(sum) / C;
+    // pass 2: variance around the mean (the row is in L1 by now)
+    const bf16* x = FUSED_RESIDUAL ? res : x1;
+    if (FUSED_RESIDUAL) __syncwarp();
+    float var = 0.f;
+    for (int p = lane; p < npack; p += 32) {
+        bf16x8 a = ld128(x + p * 8);
+        #pragma unroll
+        for (int e = 0; e < 8; e++) { float d = __bfloat162float(a[e]) - mean; var += d * d; }
+    }
+    const float rstd = rsqrtf(warp_sum(var) / C + 1e-5f);
+    // pass 3: normalise
+    bf16* o = out + (size_t)row * C;
+    for (int p = lane; p < npack; p += 32) {
+        bf16x8 a = ld128(x + p * 8);
+        bf16x8 w = ld128(weight + p * 8);
+        bf16x8 b = ld128(bias + p * 8);
+        bf16x8 r;
+        #pragma unroll
+        for (int e = 0; e < 8; e++) {
+            float n = (__bfloat162float(a[e]) - mean) * rstd;
+            r[e] = __float2bfloat16_rn(n * __bfloat162float(w[e]) + __bfloat162float(b[e]));
+        }
+        st128cs(o + p * 8, r);
+    }
+    if (lane == 0) {
+        if (mean_out) mean_out[row] = mean;
+        if (rstd_out) rstd_out[row] = rstd;
+    }
+}
+
+// dinp (+)= LN'(dout); per-CTA fp32 partials of dweight/dbias -> partials[cta][2][C]
+template <bool ACCUM_DINP>
+__global__ void __launch_bounds__(256)
+ln_bwd_kernel(bf16* __restrict__ dinp, float* __restrict__ partials, const bf16* __restrict__ dout,
+              const bf16* __restrict__ inp, const bf16* __restrict__ weight,
+              const float* __restrict__ mean, const float* __restrict__ rstd, int N, int C, int rows_per_cta) {
+    extern __shared__ float sh[];   // [warps][2][slab] only during the fold
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    const int row0 = blockIdx.x * rows_per_cta;
+    const int row1 = min(N, row0 + rows_per_cta);
+    const int npack = C >> 3;
+    const int slab_packs = 32 * MAXP;
+    float* part = partials + (size_t)blockIdx.x * 2 * C;
+
+    for (int slab0 = 0; slab0 < npack; slab0 += slab_packs) {
+        float dw[MAXP][8], db[MAXP][8];
+        #pragma unroll
+        for (int i = 0; i < MAXP; i++)
+            #pragma unroll
+            for (int e = 0; e < 8; e++) { dw[i][e] = 0.f; db[i][e] = 0.f; }
+
+        for (int row = row0 + warp; row < row1; row += nwarps) {
+            const bf16* dy = dout + (size_t)row * C;
+            const bf16* x = inp + (size_t)row * C;
+            const float m = mean[row], rs = rstd[row];
+            // row-wide sums (needed for every slab)
+            float s1 = 0.f, s2 = 0.f;
+            for (int p = lane; p < npack; p += 32) {
+                bf16x8 d = ld128(dy + p * 8), a = ld128(x + p * 8), w = ld128(weight + p * 8);
+                #pragma unroll
+                for (int e = 0; e < 8; e++) {
+                    float dn = __bfloat162float(d[e]) * __bfloat162float(w[e]);
+                    float nn = (__bfloat162float(a[e]) - m) * rs;
+                    s1 += dn; s2 += dn * nn;
+                }
+            }
+            s1 = warp_sum(s1) / C; s2 = warp_sum(s2) / C;
+            bf16* dx = dinp + (size_t)row * C;
+            #pragma unroll
+            for (int i = 0; i < MAXP; i++) {
+                const int p = slab0 + lane + 32 * i;
+                if (p < npack) {
+                    bf16x8 d = ld128(dy + p * 8), a = ld128(x + p * 8), w = ld128(weight + p * 8);
+                    bf16x8 o;
+                    if (ACCUM_DINP) o = ld128(dx + p * 8);
+                    #pragma unroll
+                    for (int e = 0; e < 8; e++) {
+                        float dyv = __bfloat162float(d[e]);
+                        float nn = (__bfloat162float(a[e]) - m) * rs;
+                        float dn = dyv * __bfloat162float(w[e]);
+                        db[i][e] += dyv;
+                        dw[i][e] += dyv * nn;
+                        float v = (dn - s1 - nn * s2) * rs;
+                        if (ACCUM_DINP) v += __bfloat162float(o[e]);
+                        o[e] = __float2bfloat16_rn(v);
+                    }
+                    st128(dx + p * 8, o);
+                }
+            }
+        }
+        // fold the warps of this CTA in warp order
+        const int slab_ch = slab_packs * 8;
+        __syncthreads();
+        #pragma unroll
+        for (int i = 0; i < MAXP; i++) {
+            const int lc = (lane + 32 * i) * 8;
+            #pragma unroll
+            for (int e = 0; e < 8; e++) {
+                sh[(warp * 2 + 0) * slab_ch + lc + e] = dw[i][e];
+                sh[(warp * 2 + 1) * slab_ch + lc + e] = db[i][e];
+            }
+        }
+        __syncthreads();
+        for (int c = threadIdx.x; c < slab_ch; c += blockDim.x) {
+            const int gc = slab0 * 8 + c;
+            if (gc < C) {
+                float a = 0.f, b = 0.f;
+                for (int w = 0; w < nwarps; w++) { a += sh[(w * 2 + 0) * slab_ch + c]; b += sh[(w * 2 + 1) * slab_ch + c]; }
+                part[gc] = a;
+                part[C + gc] = b;
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// dweight[c] (+)= sum over CTAs (in CTA order) of partials; same for dbias
+__global__ void ln_bwd_fold_kernel(bf16* __restrict__ dweight, bf16* __restrict__ dbias, const float* __restrict__ partials,
+                                   int num_ctas, int C, int accumulate) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    float a = 0.f, b = 0.f;
+    for (int i = 0; i < num_ctas; i++) {
+        a += partials[(size_t)i * 2 * C + c];
+        b += partials[(size_t)i * 2 * C + C + c];
+    }
+    if (accumulate) { a += __bfloat162float(dweight[c]); b += __bfloat162float(dbias[c]); }
+    dweight[c] = __float2bfloat16_rn(a);
+    dbias[c] = __float2bfloat16_rn(b);
+}
+
+}  // namespace
+
+extern "C" int llmc_layernorm_fwd(bf16* out, float* mean, float* rstd, const bf16* inp, const bf16* weight, const bf16* bias,
+                                  int N, int C, cudaStream_t stream) {
+    if (C % 8) return -1;
+    ln_fwd_kernel<false><<<CEIL_DIV(N, 8), 256, 0, stream>>>(out, mean, rstd, nullptr, inp, nullptr, weight, bias, N, C);
+    CUDA_CHECK(cudaGetLastError());
+    return 0;
+}
+
+// residual = inp1 + inp2 ; normed = LN(residual)
+extern "C" int llmc_fused_residual_fwd(bf16* residual, bf16* normed, float* mean, float* rstd, const bf16* inp1, const bf16* inp2,
+                                       const bf16* weight, const bf16* bias, int N, int C, cudaStream_t stream) {
+    if (C % 8) return -1;
+    ln_fwd_kernel<true><<<CEIL_DIV(N, 8), 256, 0, stream>>>(normed, mean, rstd, residual, inp1, inp2, weight, bias, N, C);
+    CUDA_CHECK(cudaGetLastError());
+    return 0;
+}
+
+// Number of fp32 scratch elements llmc_layernorm_bwd needs
+extern "C" long long llmc_layernorm_bwd_scratch(int N, int C) {
+    int sms = llmc_device_sm_count(); if (sms <= 0) sms = 148;
+    return (long long)(2 * sms) * 2 * C;
+}
+
+// dinp (+)= dLN ; dweight, dbias (+)= column sums.  `scratch` holds llmc_layernorm_bwd_scratch floats.
+extern "C" int llmc_layernorm_bwd(bf16* dinp, bf16* dweight, bf16* dbias, float* scratch, const bf16* dout, const bf16* inp,
+                                  const bf16* weight, const float* mean, const float* rstd, int N, int C,
+                                  int accumulate_dinp, int accumulate_dwdb, cudaStream_t stream) {
+    if (C % 8) return -1;
+    int sms = llmc_device_sm_count(); if (sms <= 0) sms = 148;
+    int ctas = 2 * sms;
+    int rows_per_cta = CEIL_DIV(N, ctas);
+    ctas = CEIL_DIV(N, rows_per_cta);
+    const int nwarps = 8;
+    size_t smem = (size_t)nwarps * 2 * (32 * MAXP * 8) * sizeof(float);   // 64 KB
+    static bool configured = false;
+    if (!configured) {
+        CUDA_CHECK(cudaFuncSetAttribute(ln_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        CUDA_CHECK(cudaFuncSetAttribute(ln_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = true;
+    }
+    if (accumulate_dinp) ln_bwd_kernel<true><<<ctas, nwarps * 32, smem, stream>>>(dinp, scratch, dout, inp, weight, mean, rstd, N, C, rows_per_cta);
+    else ln_bwd_kernel<false><<<ctas, nwarps * 32, smem, stream>>>(dinp, scratch, dout, inp, weight, mean, rstd, N, C, rows_per_cta);
+    CUDA_CHECK(cudaGetLastError());
+    ln_bwd_fold_kernel<<<CEIL_DIV(C, 128), 128, 0, stream>>>(dweight, dbias, scratch, ctas, C, accumulate_dwdb);
+    CUDA_CHECK(cudaGetLastError());
+    return 0;
+}

@@ -1,0 +1,238 @@
+"""Thin launchers of the sm_100a kernels: tensors in, C entry points out (see csrc/*.cu)."""
+import ctypes
+
+import torch
+
+from .. import _lib
+from .._lib import TensorTable, check
+
+MODE_STORE, MODE_GELU, MODE_DGELU, MODE_ACCUM = 0, 1, 2, 3
+
+_launches = 0   # number of kernel-library launches issued (bench.py reports it)
+
+
+def launch_count():
+    return _launches
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _p(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else ctypes.c_void_p(0)
+
+
+class _Scratch:
+    """Per-device scratch buffers that grow to the largest request and are then reused."""
+
+    def __init__(self):
+        self.bufs = {}
+
+    def get(self, key, numel, dtype, device, zero=False):
+        k = (key, device.index, dtype)
+        t = self.bufs.get(k)
+        if t is None or t.numel() < numel:
+            t = (torch.zeros if zero else torch.empty)(max(int(numel), 1), dtype=dtype, device=device)
+            self.bufs[k] = t
+        return t
+
+
+_scratch = _Scratch()
+_sm_count = {}
+
+
+def sm_count(device):
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _sm_count:
+        _sm_count[idx] = torch.cuda.get_device_properties(idx).multi_processor_count
+    return _sm_count[idx]
+
+
+def gemm(a, b, d, M, N, K, lda, ldb, ldd, a_mn, b_mn, mode, bias=None, aux=None, accumulate=False, splits=1, max_ctas=0):
+    global _launches
+    lib = _lib.cuda()
+    ws = cnt = None
+    if mode == MODE_ACCUM and splits > 1:
+        wsf = ctypes.c_longlong(0)
+        nc = ctypes.c_int(0)
+        lib.llmc_gemm_workspace(M, N, splits, ctypes.byref(wsf), ctypes.byref(nc))
+        ws = _scratch.get("gemm_ws", wsf.value, torch.float32, d.device)
+        cnt = _scratch.get("gemm_cnt", nc.value, torch.int32, d.device, zero=True)
+    _launches += 1
+    check(lib.llmc_gemm(_p(a), _p(b), _p(d), _p(bias), _p(aux), M, N, K, lda, ldb, ldd, int(a_mn), int(b_mn), mode,
+                        int(accumulate), splits, _p(ws), _p(cnt), max_ctas, _stream()), "llmc_gemm")
+
+
+def matmul_forward(out, inp, weight, bias=None, pre_gelu=None):
+    """out[M,OC] = inp[M,C] @ weight[OC,C]^T (+ bias).  With ``pre_gelu`` the pre-activation is stored there and
+    ``out`` receives its tanh-GELU (reference: matmul_forward_cublaslt, llmc/matmul.cuh:230-242)."""
+    M, C = inp.shape
+    OC = weight.shape[0]
+    mode = MODE_GELU if pre_gelu is not None else MODE_STORE
+    gemm(inp, weight, out, M, OC, C, C, C, OC, 0, 0, mode, bias=bias, aux=pre_gelu)
+
+
+def matmul_dgrad(dinp, dout, weight, pre_gelu=None):
+    """dinp[M,C] = dout[M,OC] @ weight[OC,C]; multiplied by GELU'(pre_gelu[M,C]) if given
+    (reference: matmul_backward dgrad with the DGELU epilogue, llmc/matmul.cuh:279-285)."""
+    M, OC = dout.shape
+    C = weight.shape[1]
+    mode = MODE_DGELU if pre_gelu is not None else MODE_STORE
+    gemm(dout, weight, dinp, M, C, OC, OC, C, C, 0, 1, mode, aux=pre_gelu)
+
+
+def matmul_wgrad(dweight, dout, inp, accumulate=True):
+    """dweight[OC,C] (+)= dout[M,OC]^T @ inp[M,C] with split-K sized to fill the SMs."""
+    M, OC = dout.shape
+    C = inp.shape[1]
+    splits = _lib.cuda().llmc_gemm_pick_splits(OC, C, M, sm_count(dout.device))
+    gemm(dout, inp, dweight, OC, C, M, OC, C, C, 1, 1, MODE_ACCUM, accumulate=accumulate, splits=splits)
+
+
+def bias_grad(dbias, dout, accumulate=True):
+    """dbias[OC] (+)= column sums of dout[M,OC]."""
+    global _launches
+    lib = _lib.cuda()
+    M, OC = dout.shape
+    s = _scratch.get("bias_grad", lib.llmc_bias_grad_scratch(M, OC), torch.float32, dout.device)
+    _launches += 2
+    check(lib.llmc_bias_grad(_p(dbias), _p(s), _p(dout), M, OC, int(accumulate), _stream()), "llmc_bias_grad")
+
+
+def encoder_forward(out, tokens, wte, wpe):
+    """out[B,T,C] = wte[tokens] + wpe[:T]."""
+    global _launches
+    B, T = tokens.shape
+    C = wte.shape[1]
+    _launches += 1
+    check(_lib.cuda().llmc_encoder_fwd(_p(out), _p(tokens), _p(wte), _p(wpe), B, T, C, _stream()), "llmc_encoder_fwd")
+
+
+def encoder_backward(dwte, dwpe, dout, tokens, accumulate_wte=True, accumulate_wpe=True, seed=0):
+    """Deterministic scatter-add of dout[B,T,C] into the embedding gradients."""
+    global _launches
+    B, T = tokens.shape
+    C = dwte.shape[1]
+    V = dwte.shape[0]
+    _launches += 2
+    check(_lib.cuda().llmc_encoder_bwd(_p(dwte), _p(dwpe), _p(dout), _p(tokens), B, T, C, V, int(accumulate_wte),
+                                       int(accumulate_wpe), seed & 0xFFFFFFFF, _stream()), "llmc_encoder_bwd")
+
+
+def layernorm_forward(out, mean, rstd, inp, weight, bias):
+    global _launches
+    N, C = inp.shape
+    _launches += 1
+    check(_lib.cuda().llmc_layernorm_fwd(_p(out), _p(mean), _p(rstd), _p(inp), _p(weight), _p(bias), N, C, _stream()),
+          "llmc_layernorm_fwd")
+
+
+def fused_residual_forward(residual, normed, mean, rstd, inp1, inp2, weight, bias):
+    """residual = inp1 + inp2; normed = LayerNorm(residual)."""
+    global _launches
+    N, C = inp1.shape
+    _launches += 1
+    check(_lib.cuda().llmc_fused_residual_fwd(_p(residual), _p(normed), _p(mean), _p(rstd), _p(inp1), _p(inp2), _p(weight),
+                                              _p(bias), N, C, _stream()), "llmc_fused_residual_fwd")
+
+
+def layernorm_backward(dinp, dweight, dbias, dout, inp, weight, mean, rstd, accumulate_dinp=True, accumulate_dwdb=True):
+    """dinp (+)= dLN(dout); dweight/dbias (+)= their gradients."""
+    global _launches
+    lib = _lib.cuda()
+    N, C = inp.shape
+    s = _scratch.get("ln_bwd", lib.llmc_layernorm_bwd_scratch(N, C), torch.float32, inp.device)
+    _launches += 2
+    check(lib.llmc_layernorm_bwd(_p(dinp), _p(dweight), _p(dbias), _p(s), _p(dout), _p(inp), _p(weight), _p(mean), _p(rstd),
+                                 N, C, int(accumulate_dinp), int(accumulate_dwdb), _stream()), "llmc_layernorm_bwd")
+
+
+def attention_forward(out, lse, qkv, B, T, NH):
+    """out (B,T,NH,HS), lse (B,NH,T) from packed qkv (B,T,3,NH,HS); causal."""
+    global _launches
+    hs = qkv.numel() // (B * T * 3 * NH)
+    _launches += 1
+    check(_lib.cuda().llmc_attention_fwd(_p(out), _p(lse), _p(qkv), B, T, NH, hs, _stream()), "llmc_attention_fwd")
+
+
+def attention_backward(dqkv, dout, qkv, out, lse, B, T, NH):
+    """dqkv (B,T,3,NH,HS) from dout, the forward inputs and statistics; deterministic."""
+    global _launches
+    hs = qkv.numel() // (B * T * 3 * NH)
+    delta = _scratch.get("attn_delta", B * NH * T, torch.float32, qkv.device)
+    _launches += 3
+    check(_lib.cuda().llmc_attention_bwd(_p(dqkv), _p(delta), _p(dout), _p(qkv), _p(out), _p(lse), B, T, NH, hs, _stream()),
+          "llmc_attention_bwd")
+
+
+def fused_classifier(logits, losses, targets, dloss, V, write_dlogits=True, accumulate_loss=False):
+    """losses[n] (+)= CE(logits[n], targets[n]); logits <- dlogits * dloss in place."""
+    global _launches
+    N, Vp = logits.shape
+    _launches += 1
+    check(_lib.cuda().llmc_fused_classifier(_p(logits), _p(losses), _p(targets), float(dloss), N, V, Vp, int(write_dlogits),
+                                            int(accumulate_loss), _stream()), "llmc_fused_classifier")
+
+
+def gelu_forward(out, inp):
+    global _launches
+    _launches += 1
+    check(_lib.cuda().llmc_gelu_fwd(_p(out), _p(inp), inp.numel(), _stream()), "llmc_gelu_fwd")
+
+
+def gelu_backward_inplace(d_inout, inp):
+    global _launches
+    _launches += 1
+    check(_lib.cuda().llmc_gelu_bwd_inplace(_p(d_inout), _p(inp), inp.numel(), _stream()), "llmc_gelu_bwd_inplace")
+
+
+def residual_add(out, a, b):
+    global _launches
+    _launches += 1
+    check(_lib.cuda().llmc_residual_add(_p(out), _p(a), _p(b), a.numel(), _stream()), "llmc_residual_add")
+
+
+def make_table(views):
+    """views: list of dicts(p_base, p_stride, o_base, o_stride, n, L, wd, seed)."""
+    tab = TensorTable()
+    assert len(views) <= 16
+    for i, v in enumerate(views):
+        t = tab.t[i]
+        t.p_base, t.p_stride, t.o_base, t.o_stride = v["p_base"], v["p_stride"], v["o_base"], v["o_stride"]
+        t.n, t.L, t.wd, t.seed = v["n"], v["L"], float(v.get("wd", 0.0)), int(v.get("seed", 0)) & 0xFFFFFFFF
+    tab.count = len(views)
+    return tab
+
+
+def global_norm_sq(out, grads, views):
+    """out[0] = sum of squares of the gradient elements described by ``views`` (deterministic)."""
+    global _launches
+    lib = _lib.cuda()
+    part = _scratch.get("norm_sq", lib.llmc_norm_sq_scratch(), torch.float32, grads.device)
+    tab = make_table(views)
+    _launches += 2
+    check(lib.llmc_global_norm_sq(_p(out), _p(part), _p(grads), ctypes.byref(tab), _stream()), "llmc_global_norm_sq")
+
+
+def adamw_update(params, master, grads, m, v, views, lr, beta1, beta2, eps, t, grad_scale=1.0, norm_sq=None, grad_clip=1.0):
+    """AdamW on the views; bf16 params are stochastically rounded from the fp32 result."""
+    global _launches
+    tab = make_table(views)
+    _launches += 1
+    check(_lib.cuda().llmc_adamw(_p(params), _p(master), _p(grads), _p(m), _p(v), ctypes.byref(tab), lr, beta1, beta2, eps,
+                                 int(t), grad_scale, _p(norm_sq), grad_clip, _stream()), "llmc_adamw")
+
+
+def params_from_master(params, master, views):
+    global _launches
+    tab = make_table(views)
+    _launches += 1
+    check(_lib.cuda().llmc_params_from_master(_p(params), _p(master), ctypes.byref(tab), _stream()), "llmc_params_from_master")
+
+
+def master_from_params(master, params, views):
+    global _launches
+    tab = make_table(views)
+    _launches += 1
+    check(_lib.cuda().llmc_master_from_params(_p(master), _p(params), ctypes.byref(tab), _stream()), "llmc_master_from_params")
