@@ -34,6 +34,7 @@ constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + NUM_EPI_BUFS * EPI_BUF_BYTES +
 constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 512;
 constexpr int RASTER_GROUP = 16;
+constexpr int MAX_SPLIT_GROUP = 8;
 
 enum EpiMode : int {
     EPI_STORE = 0,      // D = acc (+ bias[n])
@@ -352,12 +353,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                             for (int j = 0; j < BN; j += 8) {
                                 if (n0 + j >= g.N) break;
                                 float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                                for (int s = 0; s < g.splits; s++) {      // fixed order: deterministic
-                                    const float* p = wt + (size_t)s * (BM * BN);
-                                    float4 a = __ldcg(reinterpret_cast<const float4*>(p + ((size_t)(j >> 2) * BM + row) * 4));
-                                    float4 b = __ldcg(reinterpret_cast<const float4*>(p + ((size_t)((j >> 2) + 1) * BM + row) * 4));
-                                    acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
-                                    acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+                                // all loads of a group of splits are issued before the adds (memory-level parallelism);
+                                // the adds run in split order: deterministic
+                                for (int s0 = 0; s0 < g.splits; s0 += MAX_SPLIT_GROUP) {
+                                    float4 va[MAX_SPLIT_GROUP], vb[MAX_SPLIT_GROUP];
+                                    #pragma unroll
+                                    for (int s = 0; s < MAX_SPLIT_GROUP; s++) {
+                                        if (s0 + s < g.splits) {
+                                            const float* p = wt + (size_t)(s0 + s) * (BM * BN);
+                                            va[s] = __ldcg(reinterpret_cast<const float4*>(p + ((size_t)(j >> 2) * BM + row) * 4));
+                                            vb[s] = __ldcg(reinterpret_cast<const float4*>(p + ((size_t)((j >> 2) + 1) * BM + row) * 4));
+                                        }
+                                    }
+                                    #pragma unroll
+                                    for (int s = 0; s < MAX_SPLIT_GROUP; s++) {
+                                        if (s0 + s < g.splits) {
+                                            acc[0] += va[s].x; acc[1] += va[s].y; acc[2] += va[s].z; acc[3] += va[s].w;
+                                            acc[4] += vb[s].x; acc[5] += vb[s].y; acc[6] += vb[s].z; acc[7] += vb[s].w;
+                                        }
+                                    }
                                 }
                                 bf16* dp = g.D + (size_t)grow * g.ldd + n0 + j;
                                 bf16x8 o;
@@ -437,7 +451,7 @@ extern "C" int llmc_gemm_pick_splits(int M, int N, int K, int sm_count) {
     int num_kb = CEIL_DIV(K, BK);
     if (tiles >= sm_count || num_kb < 16) return 1;
     int best = 1; double best_eff = 0.0;
-    for (int s = 1; s <= 32 && s * 8 <= num_kb; s++) {
+    for (int s = 1; s <= 8 && s * 8 <= num_kb; s++) {
         int work = tiles * s;
         int waves = CEIL_DIV(work, sm_count);
         double eff = (double)work / ((double)waves * sm_count);

@@ -5,7 +5,7 @@ import math
 import pytest
 import torch
 
-from llmc_b200.ops import kernels as K
+from llmc_b200.ops import kernels as KN
 from llmc_b200.ops import reference as R
 
 pytestmark = pytest.mark.gpu
@@ -32,7 +32,7 @@ GEMM_SHAPES = [(256, 256, 64), (128, 512, 256), (384, 768, 768), (200, 264, 136)
 def test_matmul_forward_bias(M, N, K):
     inp, w, b = rnd(M, K), rnd(N, K, scale=0.05), rnd(N)
     out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
-    K.matmul_forward(out, inp.to(DEV), w.to(DEV), b.to(DEV))
+    KN.matmul_forward(out, inp.to(DEV), w.to(DEV), b.to(DEV))
     ref = torch.empty(M, N)
     R.matmul_forward(ref, inp, w, b)
     close(out, ref, 2e-2, 1e-2, "matmul_forward")
@@ -43,7 +43,7 @@ def test_matmul_forward_nobias_canary():
     inp, w = rnd(M, K_), rnd(N, K_, scale=0.05)
     # canary rows after the output must stay untouched
     buf = torch.full((M + 8, N), 7.0, dtype=torch.bfloat16, device=DEV)
-    K.matmul_forward(buf[:M], inp.to(DEV), w.to(DEV), None)
+    KN.matmul_forward(buf[:M], inp.to(DEV), w.to(DEV), None)
     ref = torch.empty(M, N)
     R.matmul_forward(ref, inp, w, None)
     close(buf[:M], ref, 2e-2, 1e-2, "matmul_forward nobias")
@@ -55,7 +55,7 @@ def test_matmul_forward_gelu(M, N, K):
     inp, w, b = rnd(M, K), rnd(N, K, scale=0.05), rnd(N)
     out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
     pre = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
-    K.matmul_forward(out, inp.to(DEV), w.to(DEV), b.to(DEV), pre_gelu=pre)
+    KN.matmul_forward(out, inp.to(DEV), w.to(DEV), b.to(DEV), pre_gelu=pre)
     ref, refpre = torch.empty(M, N), torch.empty(M, N)
     R.matmul_forward(ref, inp, w, b, pre_gelu=refpre)
     close(pre, refpre, 2e-2, 1e-2, "pre_gelu")
@@ -66,7 +66,7 @@ def test_matmul_forward_gelu(M, N, K):
 def test_matmul_dgrad(M, OC, C):
     dout, w = rnd(M, OC), rnd(OC, C, scale=0.05)
     dinp = torch.empty(M, C, dtype=torch.bfloat16, device=DEV)
-    K.matmul_dgrad(dinp, dout.to(DEV), w.to(DEV))
+    KN.matmul_dgrad(dinp, dout.to(DEV), w.to(DEV))
     ref = torch.empty(M, C)
     R.matmul_dgrad(ref, dout, w)
     close(dinp, ref, 3e-2, 1e-2, "dgrad")
@@ -76,7 +76,7 @@ def test_matmul_dgrad_dgelu():
     M, OC, C = 384, 768, 3072
     dout, w, pre = rnd(M, OC), rnd(OC, C, scale=0.05), rnd(M, C)
     dinp = torch.empty(M, C, dtype=torch.bfloat16, device=DEV)
-    K.matmul_dgrad(dinp, dout.to(DEV), w.to(DEV), pre_gelu=pre.to(DEV))
+    KN.matmul_dgrad(dinp, dout.to(DEV), w.to(DEV), pre_gelu=pre.to(DEV))
     ref = torch.empty(M, C)
     R.matmul_dgrad(ref, dout, w, pre_gelu=pre)
     close(dinp, ref, 3e-2, 1e-2, "dgrad+dgelu")
@@ -88,13 +88,13 @@ def test_matmul_wgrad(M, OC, C, acc):
     dout, inp = rnd(M, OC, scale=0.1), rnd(M, C)
     dw0 = rnd(OC, C)
     dw = dw0.to(DEV).clone()
-    K.matmul_wgrad(dw, dout.to(DEV), inp.to(DEV), accumulate=acc)
+    KN.matmul_wgrad(dw, dout.to(DEV), inp.to(DEV), accumulate=acc)
     ref = dw0.float().clone()
     R.matmul_wgrad(ref, dout, inp, accumulate=acc)
     close(dw, ref, 5e-2, 1.5e-2, "wgrad")
     # run-twice determinism (split-K folds partials in a fixed order)
     dw2 = dw0.to(DEV).clone()
-    K.matmul_wgrad(dw2, dout.to(DEV), inp.to(DEV), accumulate=acc)
+    KN.matmul_wgrad(dw2, dout.to(DEV), inp.to(DEV), accumulate=acc)
     assert torch.equal(dw, dw2)
 
 
@@ -102,7 +102,7 @@ def test_bias_grad():
     M, OC = 1000, 776
     dout, db0 = rnd(M, OC), rnd(OC)
     db = db0.to(DEV).clone()
-    K.bias_grad(db, dout.to(DEV), accumulate=True)
+    KN.bias_grad(db, dout.to(DEV), accumulate=True)
     ref = db0.float().clone()
     R.bias_grad(ref, dout, accumulate=True)
     close(db, ref, 5e-2, 1e-2, "bias_grad")
@@ -114,7 +114,7 @@ def test_layernorm_forward_backward(N, C):
     out = torch.empty(N, C, dtype=torch.bfloat16, device=DEV)
     mean = torch.empty(N, device=DEV)
     rstd = torch.empty(N, device=DEV)
-    K.layernorm_forward(out, mean, rstd, x.to(DEV), w.to(DEV), b.to(DEV))
+    KN.layernorm_forward(out, mean, rstd, x.to(DEV), w.to(DEV), b.to(DEV))
     ro, rm, rr = torch.empty(N, C), torch.empty(N), torch.empty(N)
     R.layernorm_forward(ro, rm, rr, x, w, b)
     close(out, ro, 2e-2, 1e-2, "ln out")
@@ -122,14 +122,14 @@ def test_layernorm_forward_backward(N, C):
     close(rstd, rr, 1e-3, 1e-3, "ln rstd")
     dx0, dw0, db0 = rnd(N, C), rnd(C), rnd(C)
     dx, dw, db = dx0.to(DEV).clone(), dw0.to(DEV).clone(), db0.to(DEV).clone()
-    K.layernorm_backward(dx, dw, db, dy.to(DEV), x.to(DEV), w.to(DEV), mean, rstd, True, True)
+    KN.layernorm_backward(dx, dw, db, dy.to(DEV), x.to(DEV), w.to(DEV), mean, rstd, True, True)
     rdx, rdw, rdb = dx0.float().clone(), dw0.float().clone(), db0.float().clone()
     R.layernorm_backward(rdx, rdw, rdb, dy, x, w, rm, rr, True, True)
     close(dx, rdx, 3e-2, 1.5e-2, "ln dx")
     close(dw, rdw, 0.15, 2e-2, "ln dw")
     close(db, rdb, 0.15, 2e-2, "ln db")
     dx2, dw2, db2 = dx0.to(DEV).clone(), dw0.to(DEV).clone(), db0.to(DEV).clone()
-    K.layernorm_backward(dx2, dw2, db2, dy.to(DEV), x.to(DEV), w.to(DEV), mean, rstd, True, True)
+    KN.layernorm_backward(dx2, dw2, db2, dy.to(DEV), x.to(DEV), w.to(DEV), mean, rstd, True, True)
     assert torch.equal(dw, dw2) and torch.equal(db, db2) and torch.equal(dx, dx2)
 
 
@@ -139,7 +139,7 @@ def test_fused_residual_forward():
     res = torch.empty(N, C, dtype=torch.bfloat16, device=DEV)
     out = torch.empty(N, C, dtype=torch.bfloat16, device=DEV)
     mean, rstd = torch.empty(N, device=DEV), torch.empty(N, device=DEV)
-    K.fused_residual_forward(res, out, mean, rstd, a.to(DEV), b2.to(DEV), w.to(DEV), b.to(DEV))
+    KN.fused_residual_forward(res, out, mean, rstd, a.to(DEV), b2.to(DEV), w.to(DEV), b.to(DEV))
     rres, ro, rm, rr = torch.empty(N, C), torch.empty(N, C), torch.empty(N), torch.empty(N)
     R.fused_residual_forward(rres, ro, rm, rr, a, b2, w, b)
     close(res, rres, 2e-2, 1e-2, "residual")
@@ -153,20 +153,20 @@ def test_encoder_forward_backward():
     tok[0, :20] = 5          # heavy collisions
     wte, wpe = rnd(V, C), rnd(T, C)
     out = torch.empty(B, T, C, dtype=torch.bfloat16, device=DEV)
-    K.encoder_forward(out, tok.to(DEV), wte.to(DEV), wpe.to(DEV))
+    KN.encoder_forward(out, tok.to(DEV), wte.to(DEV), wpe.to(DEV))
     ro = torch.empty(B, T, C)
     R.encoder_forward(ro, tok, wte, wpe)
     close(out, ro, 2e-2, 1e-2, "encoder fwd")
     dout = rnd(B, T, C)
     dwte0, dwpe0 = rnd(V, C), rnd(T, C)
     dwte, dwpe = dwte0.to(DEV).clone(), dwpe0.to(DEV).clone()
-    K.encoder_backward(dwte, dwpe, dout.to(DEV), tok.to(DEV), True, True, seed=11)
+    KN.encoder_backward(dwte, dwpe, dout.to(DEV), tok.to(DEV), True, True, seed=11)
     rwte, rwpe = dwte0.float().clone(), dwpe0.float().clone()
     R.encoder_backward(rwte, rwpe, dout, tok, True, True)
     close(dwte, rwte, 8e-2, 2e-2, "dwte")      # stochastic rounding: one bf16 ulp
     close(dwpe, rwpe, 8e-2, 2e-2, "dwpe")
     dwte2, dwpe2 = dwte0.to(DEV).clone(), dwpe0.to(DEV).clone()
-    K.encoder_backward(dwte2, dwpe2, dout.to(DEV), tok.to(DEV), True, True, seed=11)
+    KN.encoder_backward(dwte2, dwpe2, dout.to(DEV), tok.to(DEV), True, True, seed=11)
     assert torch.equal(dwte, dwte2) and torch.equal(dwpe, dwpe2)
 
 
@@ -178,7 +178,7 @@ def test_encoder_backward_many_hits():
     dout = rnd(B, T, C, scale=0.1)
     dwte = torch.zeros(V, C, dtype=torch.bfloat16, device=DEV)
     dwpe = torch.zeros(T, C, dtype=torch.bfloat16, device=DEV)
-    K.encoder_backward(dwte, dwpe, dout.to(DEV), tok.to(DEV), False, False, seed=3)
+    KN.encoder_backward(dwte, dwpe, dout.to(DEV), tok.to(DEV), False, False, seed=3)
     rwte, rwpe = torch.zeros(V, C), torch.zeros(T, C)
     R.encoder_backward(rwte, rwpe, dout, tok, False, False)
     close(dwte, rwte, 0.15, 3e-2, "dwte multi-round")
@@ -192,7 +192,7 @@ def test_fused_classifier(N, V, Vp):
     tgt = torch.randint(0, V, (N,), generator=g, dtype=torch.int32)
     lg = logits.to(DEV).clone()
     losses = torch.zeros(N, device=DEV)
-    K.fused_classifier(lg, losses, tgt.to(DEV), 1.0 / N, V, True, False)
+    KN.fused_classifier(lg, losses, tgt.to(DEV), 1.0 / N, V, True, False)
     rl, rloss = logits.float().clone(), torch.zeros(N)
     R.fused_classifier(rl, rloss, tgt, 1.0 / N, V, True, False)
     close(losses, rloss, 2e-3, 1e-3, "loss")
@@ -204,16 +204,16 @@ def test_gelu_and_residual():
     n = 8 * 1000
     x, d = rnd(n), rnd(n, seed=5)
     out = torch.empty(n, dtype=torch.bfloat16, device=DEV)
-    K.gelu_forward(out, x.to(DEV))
+    KN.gelu_forward(out, x.to(DEV))
     ro = torch.empty(n)
     R.gelu_forward(ro, x)
     close(out, ro, 1e-2, 1e-2, "gelu")
     dd = d.to(DEV).clone()
-    K.gelu_backward_inplace(dd, x.to(DEV))
+    KN.gelu_backward_inplace(dd, x.to(DEV))
     rd = d.float().clone()
     R.gelu_backward_inplace(rd, x)
     close(dd, rd, 1e-2, 1e-2, "gelu bwd")
-    K.residual_add(out, x.to(DEV), d.to(DEV))
+    KN.residual_add(out, x.to(DEV), d.to(DEV))
     close(out, x.float() + d.float(), 2e-2, 1e-2, "residual add")
 
 
@@ -226,16 +226,16 @@ def test_global_norm_and_adamw():
     p0, g = rnd(n, scale=0.02), rnd(n, scale=0.01, seed=7)
     views = _views(n, L=4)
     out = torch.zeros(1, device=DEV)
-    K.global_norm_sq(out, g.to(DEV), views)
+    KN.global_norm_sq(out, g.to(DEV), views)
     ref = (g.float() ** 2).sum()
     assert abs(out.item() - ref.item()) <= 1e-4 * ref.item()
     params = p0.to(DEV).clone()
     master = torch.empty(n, device=DEV)
-    K.master_from_params(master, params, views)
+    KN.master_from_params(master, params, views)
     assert torch.equal(master.cpu(), p0.float())
     m, v = torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
     nsq = torch.tensor([ref.item()], device=DEV)
-    K.adamw_update(params, master, g.to(DEV), m, v, views, 1e-3, 0.9, 0.95, 1e-8, 1, 1.0, nsq, 0.05)
+    KN.adamw_update(params, master, g.to(DEV), m, v, views, 1e-3, 0.9, 0.95, 1e-8, 1, 1.0, nsq, 0.05)
     rp, rm, rv, rmaster = p0.float().clone(), torch.zeros(n), torch.zeros(n), p0.float().clone()
     R.adamw_update(rp, rmaster, g, rm, rv, views, 1e-3, 0.9, 0.95, 1e-8, 1, 1.0, torch.tensor([ref.item()]), 0.05)
     close(master, rmaster, 1e-6, 1e-5, "master")
@@ -247,7 +247,7 @@ def test_global_norm_and_adamw():
     assert abs(diff.mean().item()) < 0.05 * ulp.mean().item()
     # same seeds -> same rounding (resume path)
     p2 = torch.empty_like(params)
-    K.params_from_master(p2, master, views)
+    KN.params_from_master(p2, master, views)
     assert torch.equal(p2, params)
 
 
@@ -257,8 +257,29 @@ def test_attention_forward(B, T, NH):
     qkv = rnd(B, T, 3 * NH * hs)
     out = torch.full((B, T, NH * hs), float("nan"), dtype=torch.bfloat16, device=DEV)
     lse = torch.empty(B, NH, T, device=DEV)
-    K.attention_forward(out, lse, qkv.to(DEV), B, T, NH)
+    KN.attention_forward(out, lse, qkv.to(DEV), B, T, NH)
     ro, rl = torch.empty(B, T, NH * hs), torch.empty(B, NH, T)
     R.attention_forward(ro, rl, qkv, B, T, NH)
     close(lse, rl, 2e-2, 1e-3, "lse")
     close(out, ro, 2e-2, 2e-2, "attention out")
+
+
+@pytest.mark.parametrize("B,T,NH", [(1, 128, 1), (2, 64, 2), (2, 384, 3), (1, 1024, 2)])
+def test_attention_backward(B, T, NH):
+    hs = 64
+    qkv = rnd(B, T, 3 * NH * hs)
+    dout = rnd(B, T, NH * hs, scale=0.5, seed=9)
+    dev_qkv = qkv.to(DEV)
+    out = torch.empty(B, T, NH * hs, dtype=torch.bfloat16, device=DEV)
+    lse = torch.empty(B, NH, T, device=DEV)
+    KN.attention_forward(out, lse, dev_qkv, B, T, NH)
+    dqkv = torch.full((B, T, 3 * NH * hs), float("nan"), dtype=torch.bfloat16, device=DEV)
+    KN.attention_backward(dqkv, dout.to(DEV), dev_qkv, out, lse, B, T, NH)
+    ro, rl = torch.empty(B, T, NH * hs), torch.empty(B, NH, T)
+    R.attention_forward(ro, rl, qkv, B, T, NH)
+    rd = torch.empty(B, T, 3 * NH * hs)
+    R.attention_backward(rd, dout, qkv, ro, rl, B, T, NH)
+    close(dqkv, rd, 4e-2, 3e-2, "dqkv")
+    dqkv2 = torch.empty_like(dqkv)
+    KN.attention_backward(dqkv2, dout.to(DEV), dev_qkv, out, lse, B, T, NH)
+    assert torch.equal(dqkv, dqkv2)
