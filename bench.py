@@ -254,8 +254,8 @@ def run_reference(a):
     cmd = [exe, "-i", os.path.join(data_dir, "synth_train_*.bin"), "-j", os.path.join(data_dir, "synth_val_*.bin"), "-e", a.model,
            "-b", str(a.batch), "-t", str(a.seq), "-d", str(a.total_batch), "-z", str(a.zero), "-c", "0.1", "-l", "6e-4", "-u", "700", "-q", "0.0",
            "-r", str(a.recompute), "-x", str(total_steps), "-v", "1000000", "-m", "1", "-s", "1000000", "-g", "2", "-h", "0", "-n", "0"]
-    if world > 1:
-        cmd += ["-pn", str(world), "-pr", str(rank), "-pg", "8", "-pi", "fs", "-pf", sync_dir]
+    # the reference's default rendezvous is MPI, which this build does not have: use its shared-file method at every N
+    cmd += ["-pn", str(world), "-pr", str(rank), "-pg", "8", "-pi", "fs", "-pf", sync_dir]
     env = dict(os.environ)
     if world > 1:
         env["CUDA_VISIBLE_DEVICES"] = env.get("CUDA_VISIBLE_DEVICES", ",".join(str(i) for i in range(8)))
@@ -269,7 +269,7 @@ def run_reference(a):
         return unavailable("the reference trainer did not finish within 3000 s")
     wall = time.perf_counter() - t0
     clocks = sampler.stop()
-    if rank == 0 and world > 1:
+    if rank == 0:
         try:
             os.remove(os.path.join(sync_dir, "ready"))
         except OSError:

@@ -1,0 +1,316 @@
+// ZeRO-1 communication inside kernels, over NVLink peer memory (no NCCL call on these paths).
+//
+// Every rank holds pointers to all ranks' gradient buffer, parameter buffer and signal buffer
+// (symmetric allocations, same layout everywhere).  Synchronisation uses 64-bit flags in the signal
+// buffers that only ever grow (the step sequence number), written with st.release.sys after a
+// system-scope fence and polled with ld.acquire.sys; every poll is bounded (FLAG_WAIT_CYCLES) and on
+// expiry the kernel records ST_FLAG_TIMEOUT in the status word, skips its work and returns.
+//
+//  reduce_scatter   (per layer, on a side stream while backward continues)  signal "my gradients of
+//                   channel c are final" to all peers, wait for theirs, then for each tensor of the layer
+//                   read this rank's 1/N shard from every peer (plain peer loads, summed in rank order in
+//                   fp32: deterministic and identical to a reduce with a fixed tree), scale by 1/N, store
+//                   the bf16 mean into the own buffer's shard, and emit per-CTA partial sums of squares
+//                   of the reduced values (the global gradient norm needs no second pass).
+//                   Replaces ncclReduceScatter(ncclAvg) + global_norm_squared of the reference
+//                   (llmc/zero.cuh:539-548, train_gpt2.cu:1002-1023).
+//  scalar all-reduce one-shot: every rank stores {sequence, value} as one 64-bit word into its slot of
+//                   every peer's signal buffer and sums the N slots in rank order.
+//  adamw_allgather  AdamW + stochastic rounding on the own shards; each rounded bf16 pack is stored to
+//                   the own parameter buffer and to every peer's (16-byte peer stores), the last CTA to
+//                   finish raises this rank's "parameters published" flag on all peers.
+//                   Replaces adamw_kernel3 + ncclAllGather (train_gpt2.cu:1101-1120 of the reference).
+//  wait_flags       tiny kernel the consumer stream runs before it first reads gathered parameters.
+#include "common.cuh"
+
+struct TensorView {        // same layout as in optim.cu
+    long long p_base, p_stride, o_base, o_stride, n;
+    int L;
+    float wd;
+    unsigned int seed;
+    int pad;
+};
+struct TensorTable {
+    TensorView t[16];
+    int count;
+};
+
+constexpr int MAX_RANKS = 8;       // one NVSwitch domain
+struct PeerPtrs {
+    void* p[MAX_RANKS];
+};
+struct SliceList {
+    long long off[16];
+    long long size[16];
+    int count;
+};
+
+#ifndef FLAG_WAIT_CYCLES
+#define FLAG_WAIT_CYCLES (20000000000ll)      // roughly 10 s
+#endif
+
+// signal buffer layout (64-bit words)
+constexpr int SIG_RS_BASE = 0;          // [channel 0..199][src rank]
+constexpr int SIG_AG = 200 * MAX_RANKS; // [src rank]
+constexpr int SIG_BARRIER = 201 * MAX_RANKS;
+constexpr int SIG_SCALAR = 202 * MAX_RANKS;     // [parity][src rank] packed {seq, float}
+constexpr int SIG_WORDS = 208 * MAX_RANKS;
+
+namespace {
+
+DEVINL void st_release_sys(unsigned long long* p, unsigned long long v) {
+    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+DEVINL unsigned long long ld_acquire_sys(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+// wait until *p >= want; false on time-out
+DEVINL bool wait_flag_ge(const unsigned long long* p, unsigned long long want, unsigned int* status, unsigned int where) {
+    long long t0 = clock64();
+    while (ld_acquire_sys(p) < want) {
+        if (clock64() - t0 > FLAG_WAIT_CYCLES) { record_error(status, ST_FLAG_TIMEOUT, where); return false; }
+        __nanosleep(200);
+    }
+    return true;
+}
+
+__global__ void __launch_bounds__(512)
+reduce_scatter_kernel(PeerPtrs grads, PeerPtrs sig, SliceList sl, int rank, int N, float scale, int channel,
+                      unsigned long long seq, float* __restrict__ norm_partials, int wait_peers, unsigned int* status) {
+    __shared__ float red[32];
+    __shared__ int ok_s;
+    unsigned long long* my_sig = reinterpret_cast<unsigned long long*>(sig.p[rank]);
+    // 1. tell every peer that this rank's gradients of `channel` are final (block 0 only)
+    if (blockIdx.x == 0 && threadIdx.x < N) {
+        __threadfence_system();
+        unsigned long long* peer = reinterpret_cast<unsigned long long*>(sig.p[threadIdx.x]);
+        st_release_sys(peer + SIG_RS_BASE + channel * MAX_RANKS + rank, seq);
+    }
+    // 2. wait for every peer's signal
+    if (threadIdx.x == 0) ok_s = 1;
+    __syncthreads();
+    if (wait_peers && threadIdx.x < N) {
+        if (!wait_flag_ge(my_sig + SIG_RS_BASE + channel * MAX_RANKS + threadIdx.x, seq, status, 0x700 + threadIdx.x)) ok_s = 0;
+    }
+    __syncthreads();
+    float acc_sq = 0.f;
+    if (ok_s) {
+        bf16* mine = reinterpret_cast<bf16*>(grads.p[rank]);
+        for (int s = 0; s < sl.count; s++) {
+            const long long shard = sl.size[s] / N;
+            const long long base = sl.off[s] + (long long)rank * shard;
+            const long long packs = shard >> 3;
+            for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < packs; i += (long long)gridDim.x * blockDim.x) {
+                float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                bf16x8 v[MAX_RANKS];
+                #pragma unroll
+                for (int p = 0; p < MAX_RANKS; p++)
+                    if (p < N) v[p] = ld128cs(reinterpret_cast<const bf16*>(grads.p[p]) + base + i * 8);
+                #pragma unroll
+                for (int p = 0; p < MAX_RANKS; p++) {       // rank order: the same sum on every run
+                    if (p < N) {
+                        #pragma unroll
+                        for (int e = 0; e < 8; e++) sum[e] += __bfloat162float(v[p][e]);
+                    }
+                }
+                bf16x8 o;
+                #pragma unroll
+                for (int e = 0; e < 8; e++) {
+                    o[e] = __float2bfloat16_rn(sum[e] * scale);
+                    const float f = __bfloat162float(o[e]);
+                    acc_sq += f * f;
+                }
+                st128(mine + base + i * 8, o);
+            }
+        }
+    }
+    acc_sq = block_sum(acc_sq, red);
+    if (threadIdx.x == 0 && norm_partials) norm_partials[blockIdx.x] = acc_sq;
+}
+
+__global__ void scalar_allreduce_kernel(PeerPtrs sig, float* __restrict__ inout, int rank, int N, unsigned long long seq,
+                                        unsigned int* status) {
+    __shared__ float vals[MAX_RANKS];
+    __shared__ int ok_s;
+    unsigned long long* my_sig = reinterpret_cast<unsigned long long*>(sig.p[rank]);
+    const int parity = (int)(seq & 1);
+    if (threadIdx.x == 0) ok_s = 1;
+    __syncthreads();
+    if (threadIdx.x < N) {
+        const unsigned long long word = (seq << 32) | (unsigned long long)__float_as_uint(inout[0]);
+        unsigned long long* peer = reinterpret_cast<unsigned long long*>(sig.p[threadIdx.x]);
+        st_release_sys(peer + SIG_SCALAR + parity * MAX_RANKS + rank, word);
+        // wait for slot threadIdx.x of my own buffer to carry this sequence number
+        const unsigned long long* slot = my_sig + SIG_SCALAR + parity * MAX_RANKS + threadIdx.x;
+        long long t0 = clock64();
+        unsigned long long w;
+        while (((w = ld_acquire_sys(slot)) >> 32) < (seq & 0xFFFFFFFFull)) {
+            if (clock64() - t0 > FLAG_WAIT_CYCLES) { record_error(status, ST_FLAG_TIMEOUT, 0x720 + threadIdx.x); ok_s = 0; break; }
+            __nanosleep(100);
+        }
+        vals[threadIdx.x] = __uint_as_float((unsigned int)(w & 0xFFFFFFFFull));
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && ok_s) {
+        float s = 0.f;
+        for (int p = 0; p < N; p++) s += vals[p];
+        inout[0] = s;
+    }
+}
+
+DEVINL unsigned int sr_position(long long idx, int layer) {
+    return (unsigned int)(idx & 511) + 198491317u * ((unsigned int)(idx & ~511ll) + (unsigned int)layer);
+}
+
+template <bool HAS_MASTER>
+__global__ void __launch_bounds__(512)
+adamw_allgather_kernel(PeerPtrs params, PeerPtrs sig, float* __restrict__ master, const bf16* __restrict__ grads,
+                       float* __restrict__ m_buf, float* __restrict__ v_buf, const TensorTable tab, int rank, int N,
+                       float lr, float beta1, float beta2, float bc1, float bc2, float eps, float grad_scale,
+                       const float* __restrict__ norm_sq, float grad_clip, unsigned long long seq,
+                       unsigned int* __restrict__ done_counter) {
+    float scale = grad_scale;
+    bool skip = false;
+    if (norm_sq != nullptr) {
+        const float nsq = norm_sq[0];
+        if (!(nsq >= 0.f) || isinf(nsq)) skip = true;      // non-finite gradient: publish the unchanged parameters
+        else { const float nrm = sqrtf(nsq); if (nrm > grad_clip) scale = grad_scale * grad_clip / nrm; }
+    }
+    bf16* mine = reinterpret_cast<bf16*>(params.p[rank]);
+    for (int ti = 0; ti < tab.count; ti++) {
+        const TensorView tv = tab.t[ti];
+        const long long packs_per_slice = tv.n >> 3;
+        const long long total = packs_per_slice * tv.L;
+        for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+            const long long l = i / packs_per_slice, pk = i - l * packs_per_slice;
+            const long long pi = tv.p_base + l * tv.p_stride + pk * 8;
+            const long long oi = tv.o_base + l * tv.o_stride + pk * 8;
+            bf16x8 out;
+            if (!skip) {
+                const bf16x8 g = ld128cs(grads + pi);
+                f32x4 m0 = ld128(m_buf + oi), m1 = ld128(m_buf + oi + 4), v0 = ld128(v_buf + oi), v1 = ld128(v_buf + oi + 4);
+                f32x4 w0, w1;
+                if (HAS_MASTER) { w0 = ld128(master + oi); w1 = ld128(master + oi + 4); }
+                else { bf16x8 pw = ld128(mine + pi);
+                       #pragma unroll
+                       for (int e = 0; e < 4; e++) { w0[e] = __bfloat162float(pw[e]); w1[e] = __bfloat162float(pw[e + 4]); } }
+                #pragma unroll
+                for (int e = 0; e < 8; e++) {
+                    float& mm = e < 4 ? m0[e] : m1[e - 4];
+                    float& vv = e < 4 ? v0[e] : v1[e - 4];
+                    float& ww = e < 4 ? w0[e] : w1[e - 4];
+                    const float gg = scale * __bfloat162float(g[e]);
+                    mm = fmaf(beta1, mm, (1.0f - beta1) * gg);
+                    vv = fmaf(beta2, vv, (1.0f - beta2) * gg * gg);
+                    const float mh = mm / bc1, vh = vv / bc2;
+                    ww = ww - lr * (mh / (sqrtf(vh) + eps) + tv.wd * ww);
+                    out[e] = stochastic_round_bf16(ww, squirrel_noise5(sr_position(pk * 8 + e, (int)l), tv.seed));
+                }
+                st128(m_buf + oi, m0); st128(m_buf + oi + 4, m1); st128(v_buf + oi, v0); st128(v_buf + oi + 4, v1);
+                if (HAS_MASTER) { st128(master + oi, w0); st128(master + oi + 4, w1); }
+            } else {
+                out = ld128(mine + pi);
+            }
+            #pragma unroll
+            for (int p = 0; p < MAX_RANKS; p++)
+                if (p < N) st128(reinterpret_cast<bf16*>(params.p[p]) + pi, out);      // own copy and every peer's
+        }
+    }
+    // publish: the last CTA to get here raises this rank's flag on every peer
+    __threadfence_system();
+    __syncthreads();
+    __shared__ int last;
+    if (threadIdx.x == 0) {
+        unsigned int prev = atomicAdd(done_counter, 1u);
+        last = (prev == gridDim.x - 1);
+        if (last) *done_counter = 0;
+    }
+    __syncthreads();
+    if (last && threadIdx.x < N) {
+        __threadfence_system();
+        unsigned long long* peer = reinterpret_cast<unsigned long long*>(sig.p[threadIdx.x]);
+        st_release_sys(peer + SIG_AG + rank, seq);
+    }
+}
+
+__global__ void wait_flags_kernel(PeerPtrs sig, int rank, int N, int base, unsigned long long seq, unsigned int* status) {
+    const unsigned long long* my_sig = reinterpret_cast<const unsigned long long*>(sig.p[rank]);
+    if (threadIdx.x < N) wait_flag_ge(my_sig + base + threadIdx.x, seq, status, 0x740 + threadIdx.x);
+}
+
+__global__ void signal_flags_kernel(PeerPtrs sig, int rank, int N, int base, unsigned long long seq) {
+    if (threadIdx.x < N) {
+        __threadfence_system();
+        unsigned long long* peer = reinterpret_cast<unsigned long long*>(sig.p[threadIdx.x]);
+        st_release_sys(peer + base + rank, seq);
+    }
+}
+
+int fill(PeerPtrs* pp, const unsigned long long* ptrs, int N) {
+    if (N < 1 || N > MAX_RANKS) return -1;
+    for (int i = 0; i < MAX_RANKS; i++) pp->p[i] = i < N ? reinterpret_cast<void*>(ptrs[i]) : nullptr;
+    return 0;
+}
+
+}  // namespace
+
+extern "C" int llmc_p2p_signal_words() { return SIG_WORDS; }
+
+// Reduce-scatter (mean) of up to 16 slices of the gradient buffers. grad_ptrs / sig_ptrs: N device pointers (one per rank).
+// Every slice size must be a multiple of 8*N. norm_partials: `ctas` floats (may be null).
+extern "C" int llmc_p2p_reduce_scatter(const unsigned long long* grad_ptrs, const unsigned long long* sig_ptrs, const long long* offs,
+                                       const long long* sizes, int count, int rank, int N, int channel, unsigned long long seq,
+                                       float* norm_partials, int ctas, int wait_peers, cudaStream_t stream) {
+    PeerPtrs g, s; SliceList sl;
+    if (fill(&g, grad_ptrs, N) || fill(&s, sig_ptrs, N) || count > 16 || channel < 0 || channel >= 200) return -1;
+    sl.count = count;
+    for (int i = 0; i < count; i++) { sl.off[i] = offs[i]; sl.size[i] = sizes[i]; if (sizes[i] % (8 * N) || offs[i] % 8) return -2; }
+    reduce_scatter_kernel<<<ctas, 512, 0, stream>>>(g, s, sl, rank, N, 1.0f / N, channel, seq, norm_partials, wait_peers, llmc_status_ptr());
+    CUDA_CHECK(cudaGetLastError());
+    return 0;
+}
+
+extern "C" int llmc_p2p_allreduce_scalar(const unsigned long long* sig_ptrs, float* inout, int rank, int N, unsigned long long seq,
+                                         cudaStream_t stream) {
+    PeerPtrs s;
+    if (fill(&s, sig_ptrs, N)) return -1;
+    scalar_allreduce_kernel<<<1, 32, 0, stream>>>(s, inout, rank, N, seq, llmc_status_ptr());
+    CUDA_CHECK(cudaGetLastError());
+    return 0;
+}
+
+extern "C" int llmc_p2p_adamw_allgather(const unsigned long long* param_ptrs, const unsigned long long* sig_ptrs, float* master,
+                                        const bf16* grads, float* m, float* v, const TensorTable* tab, int rank, int N,
+                                        float lr, float beta1, float beta2, float eps, int t, float grad_scale, const float* norm_sq,
+                                        float grad_clip, unsigned long long seq, unsigned int* done_counter, int ctas, cudaStream_t stream) {
+    PeerPtrs p, s;
+    if (fill(&p, param_ptrs, N) || fill(&s, sig_ptrs, N)) return -1;
+    for (int i = 0; i < tab->count; i++) if (tab->t[i].n % 8 || tab->t[i].p_base % 8 || tab->t[i].p_stride % 8 || tab->t[i].o_base % 8 || tab->t[i].o_stride % 8) return -2;
+    const float bc1 = 1.0f - powf(beta1, (float)t), bc2 = 1.0f - powf(beta2, (float)t);
+    if (master) adamw_allgather_kernel<true><<<ctas, 512, 0, stream>>>(p, s, master, grads, m, v, *tab, rank, N, lr, beta1, beta2, bc1, bc2, eps, grad_scale, norm_sq, grad_clip, seq, done_counter);
+    else adamw_allgather_kernel<false><<<ctas, 512, 0, stream>>>(p, s, master, grads, m, v, *tab, rank, N, lr, beta1, beta2, bc1, bc2, eps, grad_scale, norm_sq, grad_clip, seq, done_counter);
+    CUDA_CHECK(cudaGetLastError());
+    return 0;
+}
+
+// which: 0 = parameters published (all-gather), 1 = barrier
+extern "C" int llmc_p2p_wait(const unsigned long long* sig_ptrs, int rank, int N, int which, unsigned long long seq, cudaStream_t stream) {
+    PeerPtrs s;
+    if (fill(&s, sig_ptrs, N)) return -1;
+    wait_flags_kernel<<<1, 32, 0, stream>>>(s, rank, N, which == 0 ? SIG_AG : SIG_BARRIER, seq, llmc_status_ptr());
+    CUDA_CHECK(cudaGetLastError());
+    return 0;
+}
+
+// Device-side barrier across ranks on `stream`: signal, then wait for everyone.
+extern "C" int llmc_p2p_barrier(const unsigned long long* sig_ptrs, int rank, int N, unsigned long long seq, cudaStream_t stream) {
+    PeerPtrs s;
+    if (fill(&s, sig_ptrs, N)) return -1;
+    signal_flags_kernel<<<1, 32, 0, stream>>>(s, rank, N, SIG_BARRIER, seq);
+    CUDA_CHECK(cudaGetLastError());
+    wait_flags_kernel<<<1, 32, 0, stream>>>(s, rank, N, SIG_BARRIER, seq, llmc_status_ptr());
+    CUDA_CHECK(cudaGetLastError());
+    return 0;
+}

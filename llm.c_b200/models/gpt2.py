@@ -89,7 +89,9 @@ def num_parameters(cfg):
 
 
 class GPT:
-    def __init__(self, cfg, device="cpu", dtype=None, recompute=1):
+    def __init__(self, cfg, device="cpu", dtype=None, recompute=1, flat_allocator=None):
+        """``flat_allocator(kind, numel, dtype)`` (kind = 'params' | 'grads') may supply the two flat buffers, e.g. from
+        symmetric memory that peer GPUs can address; by default they are ordinary tensors."""
         self.cfg = cfg
         self.device = torch.device(device)
         if dtype is None:
@@ -107,7 +109,11 @@ class GPT:
         for name, shape in self.shapes:
             self.offsets[name] = off
             off += math.prod(shape)
-        self.params_flat = torch.zeros(self.num_parameters, dtype=dtype, device=self.device)
+        self._flat_allocator = flat_allocator
+        if flat_allocator is not None:
+            self.params_flat = flat_allocator("params", self.num_parameters, dtype)
+        else:
+            self.params_flat = torch.zeros(self.num_parameters, dtype=dtype, device=self.device)
         self.grads_flat = None
         self.params = self._views(self.params_flat)
         self.grads = None
@@ -157,7 +163,10 @@ class GPT:
     # ------------------------------------------------------------------ buffers
     def allocate_grads(self):
         if self.grads_flat is None:
-            self.grads_flat = torch.zeros(self.num_parameters, dtype=self.dtype, device=self.device)
+            if self._flat_allocator is not None:
+                self.grads_flat = self._flat_allocator("grads", self.num_parameters, self.dtype)
+            else:
+                self.grads_flat = torch.zeros(self.num_parameters, dtype=self.dtype, device=self.device)
             self.grads = self._views(self.grads_flat)
 
     def allocate_activations(self, B, T):

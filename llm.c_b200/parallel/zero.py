@@ -162,6 +162,9 @@ class ShardedAdamW:
         """Device tensor holding the squared norm of the (reduced) gradient over all ranks."""
         if self.N > 1:
             self.backend.finish_reduce()
+        if self.sharded and hasattr(self.backend, "fused_norm_sq"):
+            self.backend.fused_norm_sq(self.norm_sq)       # partial sums were produced by the reduce-scatter kernels
+            return self.norm_sq
         ops.global_norm_sq(self.norm_sq, self.model.grads_flat, self.views())
         if self.sharded:
             self.backend.all_reduce_scalar_sum(self.norm_sq)
@@ -174,8 +177,19 @@ class ShardedAdamW:
         self.rng_state_last_update = self.sampler.state.value
         seeds = [self.sampler.random_u32() for _ in self.base_views]
         views = self.views(weight_decay, seeds)
+        fused = self.sharded and hasattr(self.backend, "adamw_allgather")
         if init_from_master_only:
             ops.params_from_master(model.params_flat, self.master, views)
+            if fused:                                      # one-off at resume: gather through the process group
+                NcclBackend(self.cfg, 1).all_gather_slices(model.params_flat, self._all_slices())
+                return
+        elif fused:
+            if self.use_master and not self.master_initialized:
+                ops.master_from_params(self.master, model.params_flat, views)
+                self.master_initialized = True
+            self.backend.adamw_allgather(self.master, self.m, self.v, views, learning_rate, self.beta1, self.beta2, self.eps, t,
+                                         grad_scale, self.norm_sq, self.grad_clip)
+            return
         else:
             if self.use_master and not self.master_initialized:
                 ops.master_from_params(self.master, model.params_flat, views)
@@ -183,7 +197,10 @@ class ShardedAdamW:
             ops.adamw_update(model.params_flat, self.master, model.grads_flat, self.m, self.v, views, learning_rate, self.beta1,
                              self.beta2, self.eps, t, grad_scale, self.norm_sq, self.grad_clip)
         if self.sharded:
-            slices = []
-            for name, off, per, L in model.tensor_sizes():
-                slices += [(off + l * per, per) for l in range(L)]
-            self.backend.all_gather_slices(model.params_flat, slices)
+            self.backend.all_gather_slices(model.params_flat, self._all_slices())
+
+    def _all_slices(self):
+        slices = []
+        for name, off, per, L in self.model.tensor_sizes():
+            slices += [(off + l * per, per) for l in range(L)]
+        return slices

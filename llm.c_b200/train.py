@@ -166,12 +166,21 @@ class Trainer:
         load = c.load_filename
         if self.resuming:
             load = checkpoint.checkpoint_paths(c.output_log_dir, self.resume_step, d.process_rank)[0]
+        # multi-GPU ZeRO-1 on this library's own NVLink kernels: the flat buffers live in symmetric memory
+        arena, sym_bufs, allocator = None, {}, None
+        if d.num_processes > 1 and self.device.type == "cuda" and (c.comm_backend or "p2p") == "p2p":
+            from .parallel import p2p
+            arena = p2p.try_create(None, d, c.zero_stage, self.print0)
+            if arena is not None:
+                def allocator(kind, numel, dt):
+                    sym_bufs[kind] = arena.alloc(numel, dt)
+                    return sym_bufs[kind][0]
         if load.endswith(".bin"):
             mcfg, _ = checkpoint.read_model_header(load)
-            self.model = gpt2.GPT(mcfg, self.device, dtype, recompute=c.recompute)
+            self.model = gpt2.GPT(mcfg, self.device, dtype, recompute=c.recompute, flat_allocator=allocator)
             checkpoint.load_model(load, self.model)
         else:
-            self.model = gpt2.GPT(gpt2.config_from_descriptor(load), self.device, dtype, recompute=c.recompute)
+            self.model = gpt2.GPT(gpt2.config_from_descriptor(load), self.device, dtype, recompute=c.recompute, flat_allocator=allocator)
             self.model.init_random(42)
         m = self.model
         if T > m.cfg.max_seq_len:
@@ -196,10 +205,10 @@ class Trainer:
 
         # ---- optimizer / parallel
         backend = None
-        if d.num_processes > 1 and self.device.type == "cuda" and (c.comm_backend or "p2p") == "p2p":
-            from .parallel import p2p
-            backend = p2p.try_create(self.model, d, c.zero_stage, self.print0)
         m.allocate_grads()
+        if arena is not None:
+            from .parallel import p2p
+            backend = p2p.P2PBackend(m, d, arena, sym_bufs["params"], sym_bufs["grads"])
         self.opt = ShardedAdamW(m, d, c.zero_stage, bool(c.use_master_weights), backend)
         self.logger = Logger(c.output_log_dir, d.process_rank, self.resuming)
         self.tokenizer = Tokenizer(c.tokenizer_path)
