@@ -25,9 +25,12 @@ class TensorTable(Structure):
 
 def _load(name, builder):
     path = os.path.join(LIBDIR, name)
-    if not os.path.exists(path):
-        from . import build as _b
-        getattr(_b, builder)()
+    from . import build as _b
+    try:
+        getattr(_b, builder)()          # no-op when the stored source hash matches
+    except Exception:
+        if not os.path.exists(path):    # no compiler on this machine and no prebuilt library
+            raise
     return ctypes.CDLL(path)
 
 

@@ -5,7 +5,7 @@
 //   1. delta[b,h,t] = sum_d O[b,t,h,d] * dO[b,t,h,d]
 //   2. "dK/dV" kernel: one CTA per (b, h, 128-row key/value tile).  K_j and V_j stay resident in
 //      shared memory while the query tiles i >= j stream through a 2-stage TMA ring.  Per query tile
-//      S = Q K^T and dP = dO V^T are formed in TMEM, the 256 softmax threads turn them into
+//      S = Q K^T and dP = dO V^T are formed in TMEM, the 512 softmax threads turn them into
 //      P = exp(S*scale - LSE) and dS = P (dP - delta) scale (bf16, swizzled shared memory), and
 //      dV += P^T dO, dK += dS^T Q accumulate in TMEM over the whole loop (MN-major A operands).
 //   3. "dQ" kernel: one CTA per (b, h, query tile); K_j, V_j stream; dQ += dS K accumulates in TMEM.
@@ -13,13 +13,15 @@
 // extra MMAs per tile and buys bit-reproducible gradients, which the reference also demands of
 // cuDNN (llmc/cudnn_att.cpp:186-191).
 //
-// A CTA has 320 threads: warp 0 TMA producer, warp 1 MMA issuer, warps 2..9 softmax/epilogue
-// (thread = one row x one 64-column half).  The softmax threads pull S/dP into registers and release
+// Both MMA kernels are persistent (one CTA per SM walks a heavy-first list of work items; resident tiles and
+// TMEM accumulators are double buffered across items).  A CTA has 576 threads: warp 0 TMA producer, warp 1 MMA issuer, warps 2..17 softmax/epilogue
+// (thread = one row x one 32-column quarter).  The softmax threads pull S/dP into registers and release
 // the TMEM tiles at once, so the next tile's S/dP MMAs run underneath the exponentials.
 //
 // Capability parity: attention_backward_cudnn (llmc/cudnn_att.cpp:256-288) and attention_backward
 // of llmc/attention.cuh in the reference.
 #include "common.cuh"
+#include <stdlib.h>
 
 int llmc_attn_qkv_map(CUtensorMap* tm, const bf16* qkv, int B, int T, int NH, int hs);   // attention_fwd.cu
 
@@ -30,8 +32,9 @@ constexpr int BT = 128;                             // tile rows (queries and ke
 constexpr int TILE_BYTES = BT * HS * 2;             // 16 KB
 constexpr int PAIR_BYTES = 2 * TILE_BYTES;          // 32 KB
 constexpr int PS_BYTES = BT * BT * 2;               // 32 KB
-constexpr int BWD_SMEM = PAIR_BYTES /*resident*/ + 2 * PAIR_BYTES /*stream*/ + 2 * PS_BYTES /*P, dS*/ + 256;
-constexpr int BWD_THREADS = 320;
+constexpr int XSTAGES = 3;                          // ring of streamed tile pairs
+constexpr int BWD_SMEM = 2 * PAIR_BYTES /*resident, double buffered*/ + XSTAGES * PAIR_BYTES /*stream*/ + 2 * PS_BYTES /*P, dS*/ + 256;
+constexpr int BWD_THREADS = 576;                   // TMA warp + MMA warp + 16 softmax warps
 constexpr int BWD_TMEM_COLS = 512;
 
 struct BwdArgs {
@@ -41,6 +44,7 @@ struct BwdArgs {
     int B, T, NH;
     float scale, scale_log2e;
     unsigned int* status;
+    int dbg;             // timing experiments only (LLMC_ATTN_DBG): 1 skip exp, 2 skip accumulate MMAs, 4 skip P/dS stores, 8 skip S/dP MMAs
 };
 
 __global__ void delta_kernel(float* __restrict__ delta, const bf16* __restrict__ out, const bf16* __restrict__ dout,
@@ -68,40 +72,52 @@ __global__ void delta_kernel(float* __restrict__ delta, const bf16* __restrict__
 
 // DKV = true : resident (K_j, V_j), streamed (Q_i, dO_i), outputs dK_j, dV_j
 // DKV = false: resident (Q_i, dO_i), streamed (K_j, V_j), output dQ_i
+// Persistent: gridDim.x CTAs (one per SM) take work items w = blockIdx.x, blockIdx.x + gridDim.x, ...; the item list is
+// ordered heavy first.  The resident pair and the TMEM accumulators are double buffered so that the loads and the first
+// MMAs of the next item run underneath the epilogue of the current one.
 template <bool DKV>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmDO, const BwdArgs a) {
     extern __shared__ __align__(1024) uint8_t smem[];
-    uint8_t* sRes = smem;                              // [2][16 KB]
-    uint8_t* sStr = sRes + PAIR_BYTES;                 // [2 stages][2][16 KB]
-    uint8_t* sP = sStr + 2 * PAIR_BYTES;
+    uint8_t* sRes = smem;                              // [2 buffers][2][16 KB]
+    uint8_t* sStr = sRes + 2 * PAIR_BYTES;             // [XSTAGES][2][16 KB]
+    uint8_t* sP = sStr + XSTAGES * PAIR_BYTES;
     uint8_t* sdS = sP + PS_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(sdS + PS_BYTES);
-    uint64_t* res_full = bars + 0;
-    uint64_t* x_full = bars + 1;      // [2]
-    uint64_t* x_empty = bars + 3;     // [2]
-    uint64_t* sdp_full = bars + 5;
-    uint64_t* sdp_empty = bars + 6;
-    uint64_t* pds_full = bars + 7;
-    uint64_t* pds_empty = bars + 8;
-    uint64_t* acc_full = bars + 9;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+    uint64_t* res_full = bars + 0;    // [2]
+    uint64_t* res_empty = bars + 2;   // [2]
+    uint64_t* x_full = bars + 4;      // [XSTAGES]
+    uint64_t* x_empty = bars + 8;     // [XSTAGES]
+    uint64_t* sdp_full = bars + 12;
+    uint64_t* sdp_empty = bars + 13;
+    uint64_t* pds_full = bars + 14;
+    uint64_t* pds_empty = bars + 15;
+    uint64_t* acc_full = bars + 16;   // [2]
+    uint64_t* acc_empty = bars + 18;  // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nt = CEIL_DIV(a.T, BT);
-    const int tile_rank = (int)(blockIdx.x / (a.B * a.NH));
-    const int bh = blockIdx.x % (a.B * a.NH);
-    const int b = bh / a.NH, h = bh % a.NH;
-    // heavy tiles first: key tile 0 sees every query tile; query tile nt-1 sees every key tile
-    const int fixed = DKV ? tile_rank : (nt - 1 - tile_rank);
-    const int cnt = DKV ? (nt - fixed) : (fixed + 1);
+    const int BH = a.B * a.NH;
+    const int total = BH * nt;
+    // work item -> (fixed tile, batch, head, number of streamed tiles); heavy items first:
+    // key tile 0 sees every query tile; query tile nt-1 sees every key tile
+    auto decode = [&](int w, int& fixed, int& b, int& h, int& cnt) {
+        const int rank = w / BH, bh = w - rank * BH;
+        fixed = DKV ? rank : (nt - 1 - rank);
+        cnt = DKV ? (nt - fixed) : (fixed + 1);
+        b = bh / a.NH; h = bh - b * a.NH;
+    };
 
     if (threadIdx.x == 0) {
         if ((smem_u32(smem) & 1023u) != 0) record_error(a.status, ST_BAD_ARG, 0x20);
-        mbar_init(res_full, 1);
-        for (int i = 0; i < 2; i++) { mbar_init(&x_full[i], 1); mbar_init(&x_empty[i], 1); }
-        mbar_init(sdp_full, 1); mbar_init(sdp_empty, 8); mbar_init(pds_full, 8); mbar_init(pds_empty, 1); mbar_init(acc_full, 1);
+        for (int i = 0; i < 2; i++) {
+            mbar_init(&res_full[i], 1); mbar_init(&res_empty[i], 1);
+            mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 16);
+        }
+        for (int i = 0; i < XSTAGES; i++) { mbar_init(&x_full[i], 1); mbar_init(&x_empty[i], 1); }
+        mbar_init(sdp_full, 1); mbar_init(sdp_empty, 16); mbar_init(pds_full, 16); mbar_init(pds_empty, 1);
         *abort_flag = 0;
         mbar_fence_init();
         tma_prefetch_desc(&tmQKV); tma_prefetch_desc(&tmDO);
@@ -111,177 +127,257 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tS = tmem_base, tdP = tmem_base + 128, tAcc0 = tmem_base + 256, tAcc1 = tmem_base + 320;
+    const uint32_t tS = tmem_base, tdP = tmem_base + 128, tAcc = tmem_base + 256;     // two accumulator buffers of 128 columns
 
     if (warp == 0) {
         if (lane == 0) {
-            // resident pair
-            mbar_expect_tx(res_full, PAIR_BYTES);
-            if (DKV) {
-                tma_load_4d(sRes, &tmQKV, res_full, 0, a.NH + h, fixed * BT, b);                   // K_j
-                tma_load_4d(sRes + TILE_BYTES, &tmQKV, res_full, 0, 2 * a.NH + h, fixed * BT, b);  // V_j
-            } else {
-                tma_load_4d(sRes, &tmQKV, res_full, 0, h, fixed * BT, b);                          // Q_i
-                tma_load_4d(sRes + TILE_BYTES, &tmDO, res_full, 0, h, fixed * BT, b);              // dO_i
-            }
-            for (int n = 0; n < cnt; n++) {
-                const int st = n & 1;
-                if (!mbar_wait(&x_empty[st], ((n >> 1) & 1) ^ 1, abort_flag, a.status, 0x600)) break;
-                uint8_t* dst = sStr + st * PAIR_BYTES;
-                mbar_expect_tx(&x_full[st], PAIR_BYTES);
+            int xst = 0; uint32_t xph = 0;                    // stream ring position of the next tile to load
+            int it = 0;
+            for (int w = blockIdx.x; w < total; w += gridDim.x, it++) {
+                int fixed, b, h, cnt; decode(w, fixed, b, h, cnt);
+                const int rb = it & 1;
+                if (!mbar_wait(&res_empty[rb], ((it >> 1) & 1) ^ 1, abort_flag, a.status, 0x601)) break;
+                uint8_t* rdst = sRes + rb * PAIR_BYTES;
+                mbar_expect_tx(&res_full[rb], PAIR_BYTES);
                 if (DKV) {
-                    const int i = fixed + n;
-                    tma_load_4d(dst, &tmQKV, &x_full[st], 0, h, i * BT, b);                        // Q_i
-                    tma_load_4d(dst + TILE_BYTES, &tmDO, &x_full[st], 0, h, i * BT, b);            // dO_i
+                    tma_load_4d(rdst, &tmQKV, &res_full[rb], 0, a.NH + h, fixed * BT, b);                   // K_j
+                    tma_load_4d(rdst + TILE_BYTES, &tmQKV, &res_full[rb], 0, 2 * a.NH + h, fixed * BT, b);  // V_j
                 } else {
-                    tma_load_4d(dst, &tmQKV, &x_full[st], 0, a.NH + h, n * BT, b);                 // K_j
-                    tma_load_4d(dst + TILE_BYTES, &tmQKV, &x_full[st], 0, 2 * a.NH + h, n * BT, b);// V_j
+                    tma_load_4d(rdst, &tmQKV, &res_full[rb], 0, h, fixed * BT, b);                          // Q_i
+                    tma_load_4d(rdst + TILE_BYTES, &tmDO, &res_full[rb], 0, h, fixed * BT, b);              // dO_i
                 }
+                bool fail = false;
+                for (int n = 0; n < cnt; n++) {
+                    const int st = xst;
+                    if (!mbar_wait(&x_empty[st], xph ^ 1, abort_flag, a.status, 0x600)) { fail = true; break; }
+                    if (++xst == XSTAGES) { xst = 0; xph ^= 1; }
+                    uint8_t* dst = sStr + st * PAIR_BYTES;
+                    if (a.dbg & 64) { mbar_arrive(&x_full[st]); continue; }
+                    mbar_expect_tx(&x_full[st], PAIR_BYTES);
+                    if (DKV) {
+                        const int i = fixed + n;
+                        tma_load_4d(dst, &tmQKV, &x_full[st], 0, h, i * BT, b);                        // Q_i
+                        tma_load_4d(dst + TILE_BYTES, &tmDO, &x_full[st], 0, h, i * BT, b);            // dO_i
+                    } else {
+                        tma_load_4d(dst, &tmQKV, &x_full[st], 0, a.NH + h, n * BT, b);                 // K_j
+                        tma_load_4d(dst + TILE_BYTES, &tmQKV, &x_full[st], 0, 2 * a.NH + h, n * BT, b);// V_j
+                    }
+                }
+                if (fail) break;
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc_s = umma_idesc_bf16(BT, BT, 0, 0);
             constexpr uint32_t idesc_acc = DKV ? umma_idesc_bf16(BT, HS, 1, 1) : umma_idesc_bf16(BT, HS, 0, 1);
-            auto issue_sdp = [&](int n) {
-                const uint32_t xs = smem_u32(sStr + (n & 1) * PAIR_BYTES), rs = smem_u32(sRes);
+            // S = Q K^T and dP = dO V^T of streamed tile t (stage t & 1) against resident buffer rb
+            auto issue_sdp = [&](int st, int rb, bool last_of_item) {
+                const uint32_t xs = smem_u32(sStr + st * PAIR_BYTES), rs = smem_u32(sRes + rb * PAIR_BYTES);
                 const uint32_t q = DKV ? xs : rs, dO = (DKV ? xs : rs) + TILE_BYTES;
                 const uint32_t k = DKV ? rs : xs, v = (DKV ? rs : xs) + TILE_BYTES;
+                if (!(a.dbg & 8)) {
                 #pragma unroll
                 for (int kk = 0; kk < HS / 16; kk++)
                     umma_ss(tS, umma_desc_sw128(q + kk * 32, 16, 1024), umma_desc_sw128(k + kk * 32, 16, 1024), idesc_s, kk > 0);
+                }
+                if (!(a.dbg & 8))
                 #pragma unroll
                 for (int kk = 0; kk < HS / 16; kk++)
                     umma_ss(tdP, umma_desc_sw128(dO + kk * 32, 16, 1024), umma_desc_sw128(v + kk * 32, 16, 1024), idesc_s, kk > 0);
                 umma_commit(sdp_full);
+                if (last_of_item) umma_commit(&res_empty[rb]);     // the resident pair is only read by these two products
             };
-            bool ok = mbar_wait(res_full, 0, abort_flag, a.status, 0x610);
-            ok = ok && mbar_wait(&x_full[0], 0, abort_flag, a.status, 0x611);
-            tc_fence_after();
-            if (ok) issue_sdp(0);
-            for (int n = 0; n < cnt && ok; n++) {
-                if (n + 1 < cnt) {
-                    if (!mbar_wait(&x_full[(n + 1) & 1], ((n + 1) >> 1) & 1, abort_flag, a.status, 0x612)) break;
-                    if (!mbar_wait(sdp_empty, n & 1, abort_flag, a.status, 0x613)) break;
-                    tc_fence_after();
-                    issue_sdp(n + 1);
-                }
-                if (!mbar_wait(pds_full, n & 1, abort_flag, a.status, 0x614)) break;
+            uint32_t t = 0;
+            int cst = 0; uint32_t cph = 0;                    // stream ring position of tile t
+            int it = 0;
+            bool ok = true;
+            if ((int)blockIdx.x < total) {
+                int fixed, b, h, cnt; decode(blockIdx.x, fixed, b, h, cnt);
+                ok = mbar_wait(&res_full[0], 0, abort_flag, a.status, 0x610) && mbar_wait(&x_full[0], 0, abort_flag, a.status, 0x611);
                 tc_fence_after();
-                const uint32_t xs = smem_u32(sStr + (n & 1) * PAIR_BYTES), rs = smem_u32(sRes);
-                const uint32_t p = smem_u32(sP), ds = smem_u32(sdS);
-                if (DKV) {
-                    // dV += P^T dO ; dK += dS^T Q : A is MN-major (two 64-wide groups 16 KB apart), K = 128 query rows
-                    #pragma unroll
-                    for (int kk = 0; kk < BT / 16; kk++)
-                        umma_ss(tAcc0, umma_desc_sw128(p + kk * 2048, BT * 128, 1024), umma_desc_sw128(xs + TILE_BYTES + kk * 2048, 8192, 1024),
-                                idesc_acc, (n > 0 || kk > 0));
-                    #pragma unroll
-                    for (int kk = 0; kk < BT / 16; kk++)
-                        umma_ss(tAcc1, umma_desc_sw128(ds + kk * 2048, BT * 128, 1024), umma_desc_sw128(xs + kk * 2048, 8192, 1024),
-                                idesc_acc, (n > 0 || kk > 0));
-                } else {
-                    // dQ += dS K : A K-major (two 64-column chunks), B = K_j as an N-major operand
-                    #pragma unroll
-                    for (int kk = 0; kk < BT / 16; kk++)
-                        umma_ss(tAcc0, umma_desc_sw128(ds + (kk >> 2) * (BT * 128) + (kk & 3) * 32, 16, 1024),
-                                umma_desc_sw128(xs + kk * 2048, 8192, 1024), idesc_acc, (n > 0 || kk > 0));
-                }
-                umma_commit(&x_empty[n & 1]);
-                umma_commit(pds_empty);
-                (void)rs;
+                if (ok) issue_sdp(0, 0, cnt == 1);
             }
-            umma_commit(acc_full);
+            for (int w = blockIdx.x; w < total && ok; w += gridDim.x, it++) {
+                int fixed, b, h, cnt; decode(w, fixed, b, h, cnt);
+                const int ab = it & 1;
+                const uint32_t acc0 = tAcc + ab * 128, acc1 = acc0 + 64;
+                for (int n = 0; n < cnt && ok; n++, t++) {
+                    // look one tile ahead (possibly into the next work item)
+                    bool have_next = true, next_new_item = false; int ncnt = cnt, nn = n + 1;
+                    if (nn == cnt) {
+                        if (w + (int)gridDim.x < total) { int f2, b2, h2; decode(w + gridDim.x, f2, b2, h2, ncnt); nn = 0; next_new_item = true; }
+                        else have_next = false;
+                    }
+                    if (have_next) {
+                        const int nit = it + (next_new_item ? 1 : 0);
+                        if (next_new_item) ok = ok && mbar_wait(&res_full[nit & 1], (nit >> 1) & 1, abort_flag, a.status, 0x615);
+                        int nst = cst + 1; uint32_t nph = cph;
+                        if (nst == XSTAGES) { nst = 0; nph ^= 1; }
+                        ok = ok && mbar_wait(&x_full[nst], nph, abort_flag, a.status, 0x612);
+                        ok = ok && mbar_wait(sdp_empty, t & 1, abort_flag, a.status, 0x613);
+                        if (!ok) break;
+                        tc_fence_after();
+                        issue_sdp(nst, nit & 1, nn == ncnt - 1);
+                    }
+                    if (n == 0) ok = ok && mbar_wait(&acc_empty[ab], ((it >> 1) & 1) ^ 1, abort_flag, a.status, 0x616);
+                    ok = ok && mbar_wait(pds_full, t & 1, abort_flag, a.status, 0x614);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t xs = smem_u32(sStr + cst * PAIR_BYTES);
+                    const uint32_t p = smem_u32(sP), ds = smem_u32(sdS);
+                    if (a.dbg & 2) {
+                    } else if (DKV) {
+                        // dV += P^T dO ; dK += dS^T Q : A is MN-major (two 64-wide groups 16 KB apart), K = 128 query rows
+                        #pragma unroll
+                        for (int kk = 0; kk < BT / 16; kk++)
+                            umma_ss(acc0, umma_desc_sw128(p + kk * 2048, BT * 128, 1024), umma_desc_sw128(xs + TILE_BYTES + kk * 2048, 8192, 1024),
+                                    idesc_acc, (n > 0 || kk > 0));
+                        #pragma unroll
+                        for (int kk = 0; kk < BT / 16; kk++)
+                            umma_ss(acc1, umma_desc_sw128(ds + kk * 2048, BT * 128, 1024), umma_desc_sw128(xs + kk * 2048, 8192, 1024),
+                                    idesc_acc, (n > 0 || kk > 0));
+                    } else {
+                        // dQ += dS K : A K-major (two 64-column chunks), B = K_j as an N-major operand
+                        #pragma unroll
+                        for (int kk = 0; kk < BT / 16; kk++)
+                            umma_ss(acc0, umma_desc_sw128(ds + (kk >> 2) * (BT * 128) + (kk & 3) * 32, 16, 1024),
+                                    umma_desc_sw128(xs + kk * 2048, 8192, 1024), idesc_acc, (n > 0 || kk > 0));
+                    }
+                    umma_commit(&x_empty[cst]);
+                    umma_commit(pds_empty);
+                    if (n == cnt - 1) umma_commit(&acc_full[ab]);
+                    if (++cst == XSTAGES) { cst = 0; cph ^= 1; }
+                }
+            }
         }
     } else {
+        // softmax / epilogue: thread = one row x one 32-column quarter of the 128 x 128 tile.
+        // These warps never leave their loops early: after an abandoned wait every later wait returns at once.
         const int q = warp & 3;                        // TMEM lane quarter
-        const int hf = (warp - 2) >> 2;                // column half handled by this thread
+        const int cq = (warp - 2) >> 2;                // column quarter handled by this thread
         const int r = q * 32 + lane;                   // row of the tile (a query row in S / dP)
         const uint32_t lane_off = (uint32_t)(q * 32) << 16;
         const float log2e = 1.4426950408889634f;
-        const size_t stat_base = ((size_t)b * a.NH + h) * a.T;
         bool ok = true;
-        for (int n = 0; n < cnt; n++) {
-            const int qi = DKV ? fixed + n : fixed;    // query tile index
-            const int kj = DKV ? fixed : n;            // key tile index
-            const int t = qi * BT + r;
-            float lse_l2 = 0.f, dlt = 0.f;
-            const bool row_ok = t < a.T;
-            if (row_ok) { lse_l2 = a.lse[stat_base + t] * log2e; dlt = a.delta[stat_base + t]; }
-            ok = mbar_wait(sdp_full, n & 1, abort_flag, a.status, 0x620) && ok;
+        uint32_t t = 0;
+        int it = 0;
+        for (int w = blockIdx.x; w < total; w += gridDim.x, it++) {
+            int fixed, b, h, cnt; decode(w, fixed, b, h, cnt);
+            const size_t stat_base = ((size_t)b * a.NH + h) * a.T;
+            float lse_l2 = 0.f, dlt_s = 0.f;           // LSE in log2 units; delta pre-multiplied by the softmax scale
+            bool row_ok;
+            {
+                const int t0 = fixed * BT + r;
+                row_ok = t0 < a.T;
+                if (row_ok) { lse_l2 = a.lse[stat_base + t0] * log2e; dlt_s = a.delta[stat_base + t0] * a.scale; }
+            }
+            for (int n = 0; n < cnt; n++, t++) {
+                const int qi = DKV ? fixed + n : fixed;    // query tile index
+                const int kj = DKV ? fixed : n;            // key tile index
+                // prefetch the next query tile's statistics (only the dK/dV kernel changes rows between tiles)
+                float nxt_lse = 0.f, nxt_dlt = 0.f; bool nxt_ok = row_ok;
+                const bool fetch_next = DKV && n + 1 < cnt;
+                if (fetch_next) {
+                    const int tn = (qi + 1) * BT + r;
+                    nxt_ok = tn < a.T;
+                    if (nxt_ok) { nxt_lse = a.lse[stat_base + tn]; nxt_dlt = a.delta[stat_base + tn]; } else { nxt_lse = 0.f; nxt_dlt = 0.f; }     // raw: converted below, after the loads had a whole tile to land
+                }
+                ok = mbar_wait(sdp_full, t & 1, abort_flag, a.status, 0x620) && ok;
+                tc_fence_after();
+                uint32_t sv[32], dv[32];
+                tmem_ld32(tS + lane_off + cq * 32, sv);
+                tmem_ld32(tdP + lane_off + cq * 32, dv);
+                tmem_ld_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(sdp_empty);      // S / dP may be overwritten by the next tile
+                uint32_t pp[16], dd[16];
+                if (qi == kj || !row_ok) {
+                    // diagonal tile (or rows past the end of the sequence): mask above the diagonal
+                    #pragma unroll
+                    for (int e = 0; e < 32; e += 2) {
+                        const int c0 = cq * 32 + e;
+                        float p0 = ex2_fast(fmaf(__uint_as_float(sv[e]), a.scale_log2e, -lse_l2));
+                        float p1 = ex2_fast(fmaf(__uint_as_float(sv[e + 1]), a.scale_log2e, -lse_l2));
+                        if (!row_ok || c0 > r) p0 = 0.f;
+                        if (!row_ok || c0 + 1 > r) p1 = 0.f;
+                        const float d0 = p0 * fmaf(__uint_as_float(dv[e]), a.scale, -dlt_s);
+                        const float d1 = p1 * fmaf(__uint_as_float(dv[e + 1]), a.scale, -dlt_s);
+                        pp[e >> 1] = pack_bf16x2(p0, p1);
+                        dd[e >> 1] = pack_bf16x2(d0, d1);
+                    }
+                } else if (a.dbg & 1) {
+                    #pragma unroll
+                    for (int e = 0; e < 32; e += 2) {
+                        const float p0 = fmaf(__uint_as_float(sv[e]), a.scale_log2e, -lse_l2);
+                        const float p1 = fmaf(__uint_as_float(sv[e + 1]), a.scale_log2e, -lse_l2);
+                        const float d0 = p0 * fmaf(__uint_as_float(dv[e]), a.scale, -dlt_s);
+                        const float d1 = p1 * fmaf(__uint_as_float(dv[e + 1]), a.scale, -dlt_s);
+                        pp[e >> 1] = pack_bf16x2(p0, p1);
+                        dd[e >> 1] = pack_bf16x2(d0, d1);
+                    }
+                } else {
+                    #pragma unroll
+                    for (int e = 0; e < 32; e += 2) {
+                        const float p0 = ex2_fast(fmaf(__uint_as_float(sv[e]), a.scale_log2e, -lse_l2));
+                        const float p1 = ex2_fast(fmaf(__uint_as_float(sv[e + 1]), a.scale_log2e, -lse_l2));
+                        const float d0 = p0 * fmaf(__uint_as_float(dv[e]), a.scale, -dlt_s);
+                        const float d1 = p1 * fmaf(__uint_as_float(dv[e + 1]), a.scale, -dlt_s);
+                        pp[e >> 1] = pack_bf16x2(p0, p1);
+                        dd[e >> 1] = pack_bf16x2(d0, d1);
+                    }
+                }
+                if (t > 0) ok = mbar_wait(pds_empty, (t - 1) & 1, abort_flag, a.status, 0x621) && ok;   // previous tile's MMAs have read P / dS
+                // 64-column chunk (cq >> 1), 16-byte units (cq & 1) * 4 .. +3 of this row, 128-byte swizzle
+                uint8_t* prow = sP + (cq >> 1) * (BT * 128) + r * 128;
+                uint8_t* drow = sdS + (cq >> 1) * (BT * 128) + r * 128;
+                if (!(a.dbg & 4))
+                #pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const int pos = ((((cq & 1) * 4) + u) ^ (r & 7)) * 16;
+                    if (DKV) *reinterpret_cast<uint4*>(prow + pos) = make_uint4(pp[u * 4], pp[u * 4 + 1], pp[u * 4 + 2], pp[u * 4 + 3]);
+                    *reinterpret_cast<uint4*>(drow + pos) = make_uint4(dd[u * 4], dd[u * 4 + 1], dd[u * 4 + 2], dd[u * 4 + 3]);
+                }
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(pds_full);
+                if (fetch_next) { lse_l2 = nxt_lse * log2e; dlt_s = nxt_dlt * a.scale; row_ok = nxt_ok; }
+            }
+            // ---- item epilogue: accumulators -> global; the MMA warp is already working on the next item
+            const int ab = it & 1;
+            ok = mbar_wait(&acc_full[ab], (it >> 1) & 1, abort_flag, a.status, 0x622) && ok;
             tc_fence_after();
-            uint32_t sv[64], dv[64];
-            tmem_ld32(tS + lane_off + hf * 64, sv);
-            tmem_ld32(tS + lane_off + hf * 64 + 32, sv + 32);
-            tmem_ld32(tdP + lane_off + hf * 64, dv);
-            tmem_ld32(tdP + lane_off + hf * 64 + 32, dv + 32);
+            uint32_t v0[16], v1[16];
+            tmem_ld16(tAcc + ab * 128 + lane_off + cq * 16, v0);
+            if (DKV) tmem_ld16(tAcc + ab * 128 + 64 + lane_off + cq * 16, v1);
             tmem_ld_wait();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(sdp_empty);      // S / dP may be overwritten by the next tile
-            const bool diag = (qi == kj);
-            uint32_t pp[32], dd[32];
-            #pragma unroll
-            for (int e = 0; e < 64; e += 2) {
-                const int c0 = hf * 64 + e;
-                float p0 = exp2f(__uint_as_float(sv[e]) * a.scale_log2e - lse_l2);
-                float p1 = exp2f(__uint_as_float(sv[e + 1]) * a.scale_log2e - lse_l2);
-                if (!row_ok || (diag && c0 > r)) p0 = 0.f;
-                if (!row_ok || (diag && c0 + 1 > r)) p1 = 0.f;
-                const float d0 = p0 * (__uint_as_float(dv[e]) - dlt) * a.scale;
-                const float d1 = p1 * (__uint_as_float(dv[e + 1]) - dlt) * a.scale;
-                pp[e >> 1] = pack_bf16x2(p0, p1);
-                dd[e >> 1] = pack_bf16x2(d0, d1);
-            }
-            if (n > 0) ok = mbar_wait(pds_empty, (n - 1) & 1, abort_flag, a.status, 0x621) && ok;   // previous tile's MMAs have read P / dS
-            uint8_t* prow = sP + hf * (BT * 128) + r * 128;
-            uint8_t* drow = sdS + hf * (BT * 128) + r * 128;
-            #pragma unroll
-            for (int u = 0; u < 8; u++) {
-                const int pos = (u ^ (r & 7)) * 16;
-                if (DKV) *reinterpret_cast<uint4*>(prow + pos) = make_uint4(pp[u * 4], pp[u * 4 + 1], pp[u * 4 + 2], pp[u * 4 + 3]);
-                *reinterpret_cast<uint4*>(drow + pos) = make_uint4(dd[u * 4], dd[u * 4 + 1], dd[u * 4 + 2], dd[u * 4 + 3]);
-            }
-            fence_async_smem();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(pds_full);
-        }
-        ok = mbar_wait(acc_full, 0, abort_flag, a.status, 0x622) && ok;
-        tc_fence_after();
-        const int t = fixed * BT + r;
-        {
-            uint32_t v0[32];
-            tmem_ld32(tAcc0 + lane_off + hf * 32, v0);
-            tmem_ld_wait();
-            if (t < a.T && ok) {
-                // DKV: acc0 = dV (slot 2); else acc0 = dQ (slot 0)
-                const int slot = DKV ? 2 : 0;
-                bf16* dst = a.dqkv + (((size_t)b * a.T + t) * 3 + slot) * a.NH * HS + (size_t)h * HS + hf * 32;
+            if (lane == 0) mbar_arrive(&acc_empty[ab]);
+            const int trow = fixed * BT + r;
+            if (trow < a.T && ok) {
+                // DKV: acc0 = dV (slot 2), acc1 = dK (slot 1); else acc0 = dQ (slot 0)
+                bf16* dst0 = a.dqkv + (((size_t)b * a.T + trow) * 3 + (DKV ? 2 : 0)) * a.NH * HS + (size_t)h * HS + cq * 16;
                 #pragma unroll
-                for (int e = 0; e < 32; e += 8) {
+                for (int e = 0; e < 16; e += 8) {
                     uint4 o;
                     o.x = pack_bf16x2(__uint_as_float(v0[e]), __uint_as_float(v0[e + 1]));
                     o.y = pack_bf16x2(__uint_as_float(v0[e + 2]), __uint_as_float(v0[e + 3]));
                     o.z = pack_bf16x2(__uint_as_float(v0[e + 4]), __uint_as_float(v0[e + 5]));
                     o.w = pack_bf16x2(__uint_as_float(v0[e + 6]), __uint_as_float(v0[e + 7]));
-                    *reinterpret_cast<uint4*>(dst + e) = o;
+                    *reinterpret_cast<uint4*>(dst0 + e) = o;
                 }
-            }
-        }
-        if (DKV) {
-            uint32_t v1[32];
-            tmem_ld32(tAcc1 + lane_off + hf * 32, v1);
-            tmem_ld_wait();
-            if (t < a.T && ok) {
-                bf16* dst = a.dqkv + (((size_t)b * a.T + t) * 3 + 1) * a.NH * HS + (size_t)h * HS + hf * 32;   // dK
-                #pragma unroll
-                for (int e = 0; e < 32; e += 8) {
-                    uint4 o;
-                    o.x = pack_bf16x2(__uint_as_float(v1[e]), __uint_as_float(v1[e + 1]));
-                    o.y = pack_bf16x2(__uint_as_float(v1[e + 2]), __uint_as_float(v1[e + 3]));
-                    o.z = pack_bf16x2(__uint_as_float(v1[e + 4]), __uint_as_float(v1[e + 5]));
-                    o.w = pack_bf16x2(__uint_as_float(v1[e + 6]), __uint_as_float(v1[e + 7]));
-                    *reinterpret_cast<uint4*>(dst + e) = o;
+                if (DKV) {
+                    bf16* dst1 = a.dqkv + (((size_t)b * a.T + trow) * 3 + 1) * a.NH * HS + (size_t)h * HS + cq * 16;
+                    #pragma unroll
+                    for (int e = 0; e < 16; e += 8) {
+                        uint4 o;
+                        o.x = pack_bf16x2(__uint_as_float(v1[e]), __uint_as_float(v1[e + 1]));
+                        o.y = pack_bf16x2(__uint_as_float(v1[e + 2]), __uint_as_float(v1[e + 3]));
+                        o.z = pack_bf16x2(__uint_as_float(v1[e + 4]), __uint_as_float(v1[e + 5]));
+                        o.w = pack_bf16x2(__uint_as_float(v1[e + 6]), __uint_as_float(v1[e + 7]));
+                        *reinterpret_cast<uint4*>(dst1 + e) = o;
+                    }
                 }
             }
         }
@@ -326,10 +422,13 @@ extern "C" int llmc_attention_bwd(bf16* dqkv, float* delta, const bf16* dout, co
     a.scale = 1.0f / sqrtf((float)hs);
     a.scale_log2e = a.scale * 1.4426950408889634f;
     a.status = llmc_status_ptr();
+    { const char* e = getenv("LLMC_ATTN_DBG"); a.dbg = e ? atoi(e) : 0; }
     const int nt = CEIL_DIV(T, BT);
-    attn_bwd_kernel<true><<<B * NH * nt, BWD_THREADS, BWD_SMEM, stream>>>(tmQKV, tmDO, a);
+    int sms = llmc_device_sm_count(); if (sms <= 0) sms = 148;
+    const int grid = B * NH * nt < sms ? B * NH * nt : sms;
+    if (!(a.dbg & 16)) attn_bwd_kernel<true><<<grid, BWD_THREADS, BWD_SMEM, stream>>>(tmQKV, tmDO, a);
     CUDA_CHECK(cudaGetLastError());
-    attn_bwd_kernel<false><<<B * NH * nt, BWD_THREADS, BWD_SMEM, stream>>>(tmQKV, tmDO, a);
+    if (!(a.dbg & 32)) attn_bwd_kernel<false><<<grid, BWD_THREADS, BWD_SMEM, stream>>>(tmQKV, tmDO, a);
     CUDA_CHECK(cudaGetLastError());
     return 0;
 }

@@ -1,13 +1,16 @@
 // Causal flash attention forward for sm_100a on the packed (B, T, 3, NH, HS) QKV layout, HS = 64.
 //
-// One CTA per (batch, head, 128-row query tile); two CTAs share an SM so that one CTA's softmax
-// overlaps the other's tensor-core work.  Roles inside a CTA (192 threads):
-//   warp 0     TMA producer: Q once, then K tiles (double buffered) and V tiles (single buffer),
-//              read in place from the packed QKV tensor through a 4-D tensor map.
-//   warp 1     MMA issuer: S = Q K^T into TMEM columns [0,128), PV = P V into TMEM columns [128,192).
-//   warps 2-5  softmax: thread r owns query row r.  Two passes over the S row in TMEM (max, then
-//              exp / row sum / bf16 P written to 128-byte-swizzled shared memory as the A operand of
-//              the PV MMA); the output row lives in 64 fp32 registers and is rescaled on line.
+// Persistent: one CTA per SM walks a heavy-first list of (batch, head, 128-row query tile) work items; Q is double
+// buffered so the next item's loads and first MMA run under the current item's tail.  Roles inside a CTA (576 threads):
+//   warp 0      TMA producer: Q once, then K and V tiles (double buffered), read in place from the
+//               packed QKV tensor through a 4-D tensor map.
+//   warp 1      MMA issuer: S = Q K^T into TMEM columns [0,128), PV = P V into one of two 64-column
+//               TMEM buffers.  S(j+1) is issued as soon as the softmax threads hold S(j) in registers.
+//   warps 2-17  softmax: thread = query row x 32-column quarter.  One TMEM load of its 32 scores, row
+//               maximum exchanged between the four quarters through shared memory, exp2 on the SFU,
+//               bf16 P written to 128-byte-swizzled shared memory (A operand of the PV MMA, double
+//               buffered); each thread owns 16 of the 64 output columns in registers and folds in the
+//               previous tile's PV while the tensor core works on the current one.
 // Statistics are written as natural-log LSE per (b, h, t), the layout cuDNN's SDPA uses in the
 // reference (llmc/cudnn_att.cpp:105-113).  Tiles above the diagonal are skipped.
 //
@@ -21,8 +24,10 @@ constexpr int HS = 64;
 constexpr int BQ = 128, BKV = 128;
 constexpr int TILE_BYTES = 128 * HS * 2;           // 16 KB: a 128 x 64 bf16 tile
 constexpr int P_BYTES = BQ * BKV * 2;              // 32 KB
-constexpr int FWD_SMEM = TILE_BYTES /*Q*/ + 2 * TILE_BYTES /*K*/ + TILE_BYTES /*V*/ + P_BYTES + 256;
-constexpr int FWD_THREADS = 192;
+constexpr int XCH_BYTES = (2 * 4 * 128 + 4 * 128) * 4;     // row-max exchange (double buffered) + final row sums
+constexpr int KVSTAGES = 3;
+constexpr int FWD_SMEM = 2 * TILE_BYTES /*Q*/ + KVSTAGES * TILE_BYTES /*K*/ + KVSTAGES * TILE_BYTES /*V*/ + 2 * P_BYTES + XCH_BYTES + 256;
+constexpr int FWD_THREADS = 576;                   // TMA warp + MMA warp + 16 softmax warps
 constexpr int FWD_TMEM_COLS = 256;
 
 struct FwdArgs {
@@ -34,38 +39,47 @@ struct FwdArgs {
     unsigned int* status;
 };
 
-__global__ void __launch_bounds__(FWD_THREADS, 2)
+DEVINL void quarter_barrier(int q) { asm volatile("bar.sync %0, 128;" ::"r"(1 + q) : "memory"); }
+
+__global__ void __launch_bounds__(FWD_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FwdArgs a) {
     extern __shared__ __align__(1024) uint8_t smem[];
-    uint8_t* sQ = smem;
-    uint8_t* sK = sQ + TILE_BYTES;             // 2 stages
-    uint8_t* sV = sK + 2 * TILE_BYTES;
-    uint8_t* sP = sV + TILE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sP + P_BYTES);
-    uint64_t* q_full = bars + 0;
-    uint64_t* k_full = bars + 1;     // [2]
-    uint64_t* k_empty = bars + 3;    // [2]
-    uint64_t* v_full = bars + 5;
-    uint64_t* s_full = bars + 6;
-    uint64_t* s_empty = bars + 7;
-    uint64_t* p_full = bars + 8;
-    uint64_t* o_full = bars + 9;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+    uint8_t* sQ = smem;                        // 2 buffers (current / next work item)
+    uint8_t* sK = sQ + 2 * TILE_BYTES;         // KVSTAGES stages
+    uint8_t* sV = sK + KVSTAGES * TILE_BYTES;  // KVSTAGES stages
+    uint8_t* sP = sV + KVSTAGES * TILE_BYTES;  // 2 buffers
+    float* xmax = reinterpret_cast<float*>(sP + 2 * P_BYTES);      // [2][4][128]
+    float* xsum = xmax + 2 * 4 * 128;                              // [4][128]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(xmax) + XCH_BYTES);
+    uint64_t* q_full = bars + 0;     // [2]
+    uint64_t* q_empty = bars + 2;    // [2]
+    uint64_t* k_full = bars + 4;     // [KVSTAGES]
+    uint64_t* k_empty = bars + 8;    // [KVSTAGES]
+    uint64_t* v_full = bars + 12;    // [KVSTAGES]
+    uint64_t* v_empty = bars + 16;   // [KVSTAGES]
+    uint64_t* s_full = bars + 20;
+    uint64_t* s_empty = bars + 21;
+    uint64_t* p_full = bars + 22;
+    uint64_t* o_full = bars + 23;    // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 25);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nq = CEIL_DIV(a.T, BQ);
-    // heavy (late) query tiles first
-    const int qi = nq - 1 - (int)(blockIdx.x / (a.B * a.NH));
-    const int bh = blockIdx.x % (a.B * a.NH);
-    const int b = bh / a.NH, h = bh % a.NH;
-    const int n_kv = qi + 1;
+    const int BH = a.B * a.NH;
+    const int total = BH * nq;
+    // persistent: work item w -> (query tile, batch, head); late (heavy) query tiles first
+    auto decode = [&](int w, int& qi, int& b, int& h) {
+        const int rank = w / BH, bh = w - rank * BH;
+        qi = nq - 1 - rank;
+        b = bh / a.NH; h = bh - b * a.NH;
+    };
 
     if (threadIdx.x == 0) {
         if ((smem_u32(smem) & 1023u) != 0) record_error(a.status, ST_BAD_ARG, 0x10);
-        mbar_init(q_full, 1);
-        for (int i = 0; i < 2; i++) { mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); }
-        mbar_init(v_full, 1); mbar_init(s_full, 1); mbar_init(s_empty, 4); mbar_init(p_full, 4); mbar_init(o_full, 1);
+        for (int i = 0; i < 2; i++) { mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 1); mbar_init(&o_full[i], 1); }
+        for (int i = 0; i < KVSTAGES; i++) { mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1); }
+        mbar_init(s_full, 1); mbar_init(s_empty, 16); mbar_init(p_full, 16);
         *abort_flag = 0;
         mbar_fence_init();
         tma_prefetch_desc(&tmQKV);
@@ -75,156 +89,196 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FwdArgs a) {
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tS = tmem_base, tO = tmem_base + 128;
+    const uint32_t tS = tmem_base, tO = tmem_base + 128;       // O partial products: two 64-column buffers
 
     if (warp == 0) {
         if (lane == 0) {
-            mbar_expect_tx(q_full, TILE_BYTES);
-            tma_load_4d(sQ, &tmQKV, q_full, 0, h, qi * BQ, b);
-            for (int j = 0; j < n_kv; j++) {
-                const int st = j & 1;
-                if (!mbar_wait(&k_empty[st], ((j >> 1) & 1) ^ 1, abort_flag, a.status, 0x500)) break;
-                mbar_expect_tx(&k_full[st], TILE_BYTES);
-                tma_load_4d(sK + st * TILE_BYTES, &tmQKV, &k_full[st], 0, a.NH + h, j * BKV, b);
-                if (j > 0) { if (!mbar_wait(o_full, (j - 1) & 1, abort_flag, a.status, 0x501)) break; }   // PV(j-1) has read V
-                mbar_expect_tx(v_full, TILE_BYTES);
-                tma_load_4d(sV, &tmQKV, v_full, 0, 2 * a.NH + h, j * BKV, b);
+            int kst = 0; uint32_t kph = 0;
+            int it = 0;
+            for (int w = blockIdx.x; w < total; w += gridDim.x, it++) {
+                int qi, b, h; decode(w, qi, b, h);
+                const int qb = it & 1;
+                if (!mbar_wait(&q_empty[qb], ((it >> 1) & 1) ^ 1, abort_flag, a.status, 0x502)) break;
+                mbar_expect_tx(&q_full[qb], TILE_BYTES);
+                tma_load_4d(sQ + qb * TILE_BYTES, &tmQKV, &q_full[qb], 0, h, qi * BQ, b);
+                bool fail = false;
+                for (int j = 0; j <= qi; j++) {
+                    const int st = kst;
+                    const uint32_t ph = kph ^ 1;
+                    if (++kst == KVSTAGES) { kst = 0; kph ^= 1; }
+                    if (!mbar_wait(&k_empty[st], ph, abort_flag, a.status, 0x500)) { fail = true; break; }
+                    mbar_expect_tx(&k_full[st], TILE_BYTES);
+                    tma_load_4d(sK + st * TILE_BYTES, &tmQKV, &k_full[st], 0, a.NH + h, j * BKV, b);
+                    if (!mbar_wait(&v_empty[st], ph, abort_flag, a.status, 0x501)) { fail = true; break; }
+                    mbar_expect_tx(&v_full[st], TILE_BYTES);
+                    tma_load_4d(sV + st * TILE_BYTES, &tmQKV, &v_full[st], 0, 2 * a.NH + h, j * BKV, b);
+                }
+                if (fail) break;
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc_s = umma_idesc_bf16(BQ, BKV, 0, 0);     // Q (K-major) x K (K-major)
             constexpr uint32_t idesc_o = umma_idesc_bf16(BQ, HS, 0, 1);      // P (K-major) x V (N-major)
-            auto issue_s = [&](int j) {
-                const uint32_t q = smem_u32(sQ), k = smem_u32(sK + (j & 1) * TILE_BYTES);
+            auto issue_s = [&](int st, int qb, bool last_of_item) {
+                const uint32_t q = smem_u32(sQ + qb * TILE_BYTES), k = smem_u32(sK + st * TILE_BYTES);
                 #pragma unroll
                 for (int kk = 0; kk < HS / 16; kk++)
                     umma_ss(tS, umma_desc_sw128(q + kk * 32, 16, 1024), umma_desc_sw128(k + kk * 32, 16, 1024), idesc_s, kk > 0);
                 umma_commit(s_full);
-                umma_commit(&k_empty[j & 1]);
+                umma_commit(&k_empty[st]);
+                if (last_of_item) umma_commit(&q_empty[qb]);
             };
-            bool ok = mbar_wait(q_full, 0, abort_flag, a.status, 0x510);
-            ok = ok && mbar_wait(&k_full[0], 0, abort_flag, a.status, 0x511);
-            tc_fence_after();
-            if (ok) issue_s(0);
-            for (int j = 0; j < n_kv && ok; j++) {
-                if (j + 1 < n_kv) {
-                    if (!mbar_wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, abort_flag, a.status, 0x512)) break;
-                    if (!mbar_wait(s_empty, j & 1, abort_flag, a.status, 0x513)) break;
-                    tc_fence_after();
-                    issue_s(j + 1);
-                }
-                if (!mbar_wait(p_full, j & 1, abort_flag, a.status, 0x514)) break;
-                if (!mbar_wait(v_full, j & 1, abort_flag, a.status, 0x515)) break;
+            uint32_t t = 0;
+            int cst = 0; uint32_t cph = 0;        // K/V ring position of tile t
+            int it = 0;
+            bool ok = true;
+            if ((int)blockIdx.x < total) {
+                int qi, b, h; decode(blockIdx.x, qi, b, h);
+                ok = mbar_wait(&q_full[0], 0, abort_flag, a.status, 0x510) && mbar_wait(&k_full[0], 0, abort_flag, a.status, 0x511);
                 tc_fence_after();
-                const uint32_t p = smem_u32(sP), v = smem_u32(sV);
-                #pragma unroll
-                for (int kk = 0; kk < BKV / 16; kk++) {
-                    // P: two 64-column swizzled chunks of 16 KB; V: 128 kv rows of 128 B, 16 rows per K step
-                    const uint32_t pa = p + (kk >> 2) * (BQ * 128) + (kk & 3) * 32;
-                    umma_ss(tO, umma_desc_sw128(pa, 16, 1024), umma_desc_sw128(v + kk * 2048, 8192, 1024), idesc_o, kk > 0);
+                if (ok) issue_s(0, 0, qi == 0);
+            }
+            for (int w = blockIdx.x; w < total && ok; w += gridDim.x, it++) {
+                int qi, b, h; decode(w, qi, b, h);
+                for (int j = 0; j <= qi && ok; j++, t++) {
+                    // S of the next tile (possibly the first tile of the next work item) as soon as S(t) sits in registers
+                    bool have_next = true, new_item = false; int nqi = qi, nj = j + 1;
+                    if (nj > qi) {
+                        if (w + (int)gridDim.x < total) { int b2, h2; decode(w + gridDim.x, nqi, b2, h2); nj = 0; new_item = true; }
+                        else have_next = false;
+                    }
+                    if (have_next) {
+                        const int nit = it + (new_item ? 1 : 0);
+                        if (new_item) ok = ok && mbar_wait(&q_full[nit & 1], (nit >> 1) & 1, abort_flag, a.status, 0x516);
+                        int nst = cst + 1; uint32_t nph = cph;
+                        if (nst == KVSTAGES) { nst = 0; nph ^= 1; }
+                        ok = ok && mbar_wait(&k_full[nst], nph, abort_flag, a.status, 0x512);
+                        ok = ok && mbar_wait(s_empty, t & 1, abort_flag, a.status, 0x513);
+                        if (!ok) break;
+                        tc_fence_after();
+                        issue_s(nst, nit & 1, nj == nqi);
+                    }
+                    ok = ok && mbar_wait(p_full, t & 1, abort_flag, a.status, 0x514);
+                    ok = ok && mbar_wait(&v_full[cst], cph, abort_flag, a.status, 0x515);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t p = smem_u32(sP + (t & 1) * P_BYTES), v = smem_u32(sV + cst * TILE_BYTES);
+                    #pragma unroll
+                    for (int kk = 0; kk < BKV / 16; kk++) {
+                        // P: two 64-column swizzled chunks of 16 KB; V: 128 kv rows of 128 B, 16 rows per K step
+                        const uint32_t pa = p + (kk >> 2) * (BQ * 128) + (kk & 3) * 32;
+                        umma_ss(tO + (t & 1) * 64, umma_desc_sw128(pa, 16, 1024), umma_desc_sw128(v + kk * 2048, 8192, 1024), idesc_o, kk > 0);
+                    }
+                    umma_commit(&o_full[t & 1]);
+                    umma_commit(&v_empty[cst]);
+                    if (++cst == KVSTAGES) { cst = 0; cph ^= 1; }
                 }
-                umma_commit(o_full);
             }
         }
     } else {
+        // softmax: thread = query row r x 32-column quarter cq of the S tile; it also owns 16 of the 64 output columns.
+        // These warps meet at named barriers, so they never leave the loops early (abandoned waits return at once).
         const int q = warp & 3;
-        const int r = q * 32 + lane;                 // query row inside the tile
+        const int cq = (warp - 2) >> 2;
+        const int r = q * 32 + lane;
         const uint32_t lane_off = (uint32_t)(q * 32) << 16;
-        float m = -INFINITY, l = 0.f;
-        float O[HS];
-        #pragma unroll
-        for (int d = 0; d < HS; d++) O[d] = 0.f;
         bool ok = true;
-        for (int j = 0; j < n_kv; j++) {
-            ok = mbar_wait(s_full, j & 1, abort_flag, a.status, 0x520) && ok;
-            tc_fence_after();
-            const bool diag = (j == qi);
-            // pass 1: row maximum
-            float mx = m;
-            #pragma unroll 1
-            for (int c = 0; c < 4; c++) {
-                uint32_t v[32];
-                tmem_ld32(tS + lane_off + c * 32, v);
-                tmem_ld_wait();
-                #pragma unroll
-                for (int e = 0; e < 32; e++) {
-                    float s = __uint_as_float(v[e]);
-                    if (diag && (c * 32 + e > r)) s = -INFINITY;
-                    mx = fmaxf(mx, s);
-                }
-            }
-            const float alpha = exp2f((m - mx) * a.scale_log2e);     // m = -inf on the first tile -> 0
-            m = mx;
-            const float moff = m * a.scale_log2e;
-            // fold in the previous tile's P V (its MMA finished while we were waiting for S)
-            if (j > 0) {
-                ok = mbar_wait(o_full, (j - 1) & 1, abort_flag, a.status, 0x521) && ok;
-                tc_fence_after();
-                #pragma unroll
-                for (int c = 0; c < 2; c++) {
-                    uint32_t v[32];
-                    tmem_ld32(tO + lane_off + c * 32, v);
-                    tmem_ld_wait();
-                    #pragma unroll
-                    for (int e = 0; e < 32; e++) O[c * 32 + e] += __uint_as_float(v[e]);
-                }
-            }
+        uint32_t t = 0;
+        for (int w = blockIdx.x; w < total; w += gridDim.x) {
+            int qi, b, h; decode(w, qi, b, h);
+            float m = -INFINITY, l = 0.f;
+            float O[16];
             #pragma unroll
-            for (int d = 0; d < HS; d++) O[d] *= alpha;
-            l *= alpha;
-            // pass 2: probabilities -> bf16 P in shared memory (A operand of the P V MMA)
-            float rs = 0.f;
-            #pragma unroll 1
-            for (int c = 0; c < 4; c++) {
+            for (int d = 0; d < 16; d++) O[d] = 0.f;
+            for (int j = 0; j <= qi; j++, t++) {
+                ok = mbar_wait(s_full, t & 1, abort_flag, a.status, 0x520) && ok;
+                tc_fence_after();
                 uint32_t v[32];
-                tmem_ld32(tS + lane_off + c * 32, v);
+                tmem_ld32(tS + lane_off + cq * 32, v);
                 tmem_ld_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(s_empty);
+                float mx = -INFINITY;
+                if (j == qi) {
+                    #pragma unroll
+                    for (int e = 0; e < 32; e++) {
+                        if (cq * 32 + e > r) v[e] = 0xff800000u;      // -inf: above the diagonal
+                        mx = fmaxf(mx, __uint_as_float(v[e]));
+                    }
+                } else {
+                    #pragma unroll
+                    for (int e = 0; e < 32; e++) mx = fmaxf(mx, __uint_as_float(v[e]));
+                }
+                // row maximum over the four column quarters
+                float* xm = xmax + (t & 1) * 512;
+                xm[cq * 128 + r] = mx;
+                quarter_barrier(q);
+                mx = fmaxf(fmaxf(xm[r], xm[128 + r]), fmaxf(xm[256 + r], xm[384 + r]));
+                const float m_new = fmaxf(m, mx);
+                const float alpha = ex2_fast((m - m_new) * a.scale_log2e);      // m = -inf on the first tile -> 0
+                m = m_new;
+                const float moff = m * a.scale_log2e;
+                float rs = 0.f;
                 uint32_t pk[16];
                 #pragma unroll
                 for (int e = 0; e < 32; e += 2) {
-                    float p0 = exp2f(__uint_as_float(v[e]) * a.scale_log2e - moff);
-                    float p1 = exp2f(__uint_as_float(v[e + 1]) * a.scale_log2e - moff);
-                    if (diag && (c * 32 + e > r)) p0 = 0.f;
-                    if (diag && (c * 32 + e + 1 > r)) p1 = 0.f;
+                    const float p0 = ex2_fast(fmaf(__uint_as_float(v[e]), a.scale_log2e, -moff));
+                    const float p1 = ex2_fast(fmaf(__uint_as_float(v[e + 1]), a.scale_log2e, -moff));
                     rs += p0 + p1;
                     pk[e >> 1] = pack_bf16x2(p0, p1);
                 }
-                uint8_t* prow = sP + (c >> 1) * (BQ * 128) + r * 128;
+                l = l * alpha + rs;
+                uint8_t* prow = sP + (t & 1) * P_BYTES + (cq >> 1) * (BQ * 128) + r * 128;
                 #pragma unroll
                 for (int u = 0; u < 4; u++) {
-                    const int unit = (c & 1) * 4 + u;      // 16-byte unit inside the 128-byte row
-                    *reinterpret_cast<uint4*>(prow + ((unit ^ (r & 7)) * 16)) = make_uint4(pk[u * 4], pk[u * 4 + 1], pk[u * 4 + 2], pk[u * 4 + 3]);
+                    const int pos = ((((cq & 1) * 4) + u) ^ (r & 7)) * 16;
+                    *reinterpret_cast<uint4*>(prow + pos) = make_uint4(pk[u * 4], pk[u * 4 + 1], pk[u * 4 + 2], pk[u * 4 + 3]);
+                }
+                fence_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(p_full);
+                // fold in the previous tile's P V (rescaled to the new maximum together with the running output)
+                if (j > 0) {
+                    ok = mbar_wait(&o_full[(t - 1) & 1], ((t - 1) >> 1) & 1, abort_flag, a.status, 0x521) && ok;
+                    tc_fence_after();
+                    uint32_t ov[16];
+                    tmem_ld16(tO + ((t - 1) & 1) * 64 + lane_off + cq * 16, ov);
+                    tmem_ld_wait();
+                    tc_fence_before();
+                    #pragma unroll
+                    for (int d = 0; d < 16; d++) O[d] = (O[d] + __uint_as_float(ov[d])) * alpha;
                 }
             }
-            l += rs;
-            tc_fence_before();
-            fence_async_smem();
-            __syncwarp();
-            if (lane == 0) { mbar_arrive(s_empty); mbar_arrive(p_full); }
-        }
-        ok = mbar_wait(o_full, (n_kv - 1) & 1, abort_flag, a.status, 0x522) && ok;
-        tc_fence_after();
-        #pragma unroll
-        for (int c = 0; c < 2; c++) {
-            uint32_t v[32];
-            tmem_ld32(tO + lane_off + c * 32, v);
-            tmem_ld_wait();
-            #pragma unroll
-            for (int e = 0; e < 32; e++) O[c * 32 + e] += __uint_as_float(v[e]);
-        }
-        const int t = qi * BQ + r;
-        if (t < a.T && ok) {
-            const float inv = 1.0f / l;
-            bf16* op = a.out + (((size_t)b * a.T + t) * a.NH + h) * HS;
-            #pragma unroll
-            for (int d = 0; d < HS; d += 8) {
-                uint4 o;
-                o.x = pack_bf16x2(O[d] * inv, O[d + 1] * inv); o.y = pack_bf16x2(O[d + 2] * inv, O[d + 3] * inv);
-                o.z = pack_bf16x2(O[d + 4] * inv, O[d + 5] * inv); o.w = pack_bf16x2(O[d + 6] * inv, O[d + 7] * inv);
-                *reinterpret_cast<uint4*>(op + d) = o;
+            // last tile of the item
+            ok = mbar_wait(&o_full[(t - 1) & 1], ((t - 1) >> 1) & 1, abort_flag, a.status, 0x522) && ok;
+            tc_fence_after();
+            {
+                uint32_t ov[16];
+                tmem_ld16(tO + ((t - 1) & 1) * 64 + lane_off + cq * 16, ov);
+                tmem_ld_wait();
+                tc_fence_before();
+                #pragma unroll
+                for (int d = 0; d < 16; d++) O[d] += __uint_as_float(ov[d]);
             }
-            a.lse[((size_t)b * a.NH + h) * a.T + t] = m * a.scale + logf(l);
+            // total row sum over the four quarters
+            xsum[cq * 128 + r] = l;
+            quarter_barrier(q);
+            l = xsum[r] + xsum[128 + r] + xsum[256 + r] + xsum[384 + r];
+            const int trow = qi * BQ + r;
+            if (trow < a.T && ok) {
+                const float inv = 1.0f / l;
+                bf16* op = a.out + (((size_t)b * a.T + trow) * a.NH + h) * HS + cq * 16;
+                #pragma unroll
+                for (int d = 0; d < 16; d += 8) {
+                    uint4 o;
+                    o.x = pack_bf16x2(O[d] * inv, O[d + 1] * inv); o.y = pack_bf16x2(O[d + 2] * inv, O[d + 3] * inv);
+                    o.z = pack_bf16x2(O[d + 4] * inv, O[d + 5] * inv); o.w = pack_bf16x2(O[d + 6] * inv, O[d + 7] * inv);
+                    *reinterpret_cast<uint4*>(op + d) = o;
+                }
+                if (cq == 0) a.lse[((size_t)b * a.NH + h) * a.T + trow] = m * a.scale + logf(l);
+            }
         }
     }
     tc_fence_before();
@@ -265,7 +319,9 @@ extern "C" int llmc_attention_fwd(bf16* out, float* lse, const bf16* qkv, int B,
     a.scale_log2e = a.scale * 1.4426950408889634f;
     a.status = llmc_status_ptr();
     const int nq = CEIL_DIV(T, BQ);
-    attn_fwd_kernel<<<B * NH * nq, FWD_THREADS, FWD_SMEM, stream>>>(tm, a);
+    int sms = llmc_device_sm_count(); if (sms <= 0) sms = 148;
+    const int grid = B * NH * nq < sms ? B * NH * nq : sms;
+    attn_fwd_kernel<<<grid, FWD_THREADS, FWD_SMEM, stream>>>(tm, a);
     CUDA_CHECK(cudaGetLastError());
     return 0;
 }

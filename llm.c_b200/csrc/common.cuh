@@ -149,6 +149,23 @@ DEVINL float gelu_tanh_grad(float x) {
     return 0.5f * (1.0f + t) + x * 0.5f * sech2 * k * (1.0f + 3.0f * 0.044715f * x * x);
 }
 
+// The same functions on the hardware tanh approximation (MUFU, relative error about 2^-11, far below
+// bf16 resolution).  Every device-side GELU in this library uses these, so a GELU output recomputed
+// from a stored pre-activation is bit-identical to the one the GEMM epilogue produced.
+// 2^x on the special-function unit (inputs here are <= 0 up to rounding, so no range handling is needed)
+DEVINL float ex2_fast(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+DEVINL float tanh_fast(float x) { float y; asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+DEVINL float gelu_fast(float x) {
+    const float k = 0.7978845608028654f;
+    return 0.5f * x * (1.0f + tanh_fast(k * (x + 0.044715f * x * x * x)));
+}
+DEVINL float gelu_grad_fast(float x) {
+    const float k = 0.7978845608028654f;
+    const float x2 = x * x;
+    const float t = tanh_fast(k * x * (1.0f + 0.044715f * x2));
+    return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * k * (1.0f + 3.0f * 0.044715f * x2);
+}
+
 // ----------------------------------------------------------------------------
 // bounded waits
 

@@ -17,7 +17,7 @@ __global__ void gelu_fwd_kernel(bf16* __restrict__ out, const bf16* __restrict__
     if (i >= npack) return;
     bf16x8 a = ld128cs(inp + i * 8), o;
     #pragma unroll
-    for (int e = 0; e < 8; e++) o[e] = __float2bfloat16_rn(gelu_tanh(__bfloat162float(a[e])));
+    for (int e = 0; e < 8; e++) o[e] = __float2bfloat16_rn(gelu_fast(__bfloat162float(a[e])));
     st128(out + i * 8, o);
 }
 
@@ -26,7 +26,7 @@ __global__ void gelu_bwd_kernel(bf16* __restrict__ d_inout, const bf16* __restri
     if (i >= npack) return;
     bf16x8 a = ld128cs(inp + i * 8), d = ld128(d_inout + i * 8), o;
     #pragma unroll
-    for (int e = 0; e < 8; e++) o[e] = __float2bfloat16_rn(gelu_tanh_grad(__bfloat162float(a[e])) * __bfloat162float(d[e]));
+    for (int e = 0; e < 8; e++) o[e] = __float2bfloat16_rn(gelu_grad_fast(__bfloat162float(a[e])) * __bfloat162float(d[e]));
     st128(d_inout + i * 8, o);
 }
 

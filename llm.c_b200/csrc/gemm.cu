@@ -8,15 +8,17 @@
 // It replaces the cuBLASLt calls of the reference (llmc/matmul.cuh:109-228 and its epilogues
 // BIAS / GELU_AUX_BIAS / DGELU, beta=1 accumulation) with hand-written tcgen05 code.
 //
-// Structure of a CTA (192 threads, one CTA per SM, tiles taken round-robin):
+// Structure of a CTA (320 threads, one CTA per SM, tiles taken round-robin):
 //   warp 0      TMA producer: fills a 4-stage ring of 128x64 (A) and 256x64 (B) bf16 tiles,
 //               128-byte swizzled, signalling `full[stage]` through complete_tx.
 //   warp 1      MMA issuer: one thread issues tcgen05.mma 128x256x16 four times per stage into one
 //               of two 256-column TMEM accumulators and commits to `empty[stage]`; after the last
 //               k-block it commits to `acc_full[buf]`.
-//   warps 2..5  epilogue: tcgen05.ld the accumulator (each warp owns 32 TMEM lanes = 32 rows), apply
-//               the epilogue, stage bf16 through swizzled shared memory and write with TMA stores,
-//               then release the accumulator (`acc_empty[buf]`) so the next tile's MMAs overlap.
+//   warps 2..9  epilogue, two groups of four warps, each group owning one 128-column half of the tile:
+//               tcgen05.ld the accumulator (a warp may touch 32 TMEM lanes = 32 rows), apply the epilogue
+//               (the pre-activation of dGELU arrives by TMA), stage bf16 through 64-byte-swizzled shared
+//               memory, write with TMA stores, then release the accumulator (`acc_empty[buf]`) so the next
+//               tile's MMAs overlap.
 // No TMA load uses cluster multicast. All waits are bounded (see common.cuh).
 #include "common.cuh"
 
@@ -27,11 +29,11 @@ constexpr int UMMA_K = 16;
 constexpr int A_STAGE_BYTES = BM * BK * 2;            // 16 KB
 constexpr int B_STAGE_BYTES = BN * BK * 2;            // 32 KB
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-constexpr int EPI_COLS = 64;                          // columns per epilogue chunk (128 B of bf16)
-constexpr int EPI_BUF_BYTES = BM * EPI_COLS * 2;      // 16 KB
-constexpr int NUM_EPI_BUFS = 2;
+constexpr int EPI_COLS = 32;                          // columns per epilogue chunk (64 B of bf16)
+constexpr int EPI_BUF_BYTES = BM * EPI_COLS * 2;      // 8 KB
+constexpr int NUM_EPI_BUFS = 4;                       // two per epilogue group
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + NUM_EPI_BUFS * EPI_BUF_BYTES + 1024 /*align*/ + 256 /*barriers*/;
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 320;
 constexpr int TMEM_COLS = 512;
 constexpr int RASTER_GROUP = 16;
 constexpr int MAX_SPLIT_GROUP = 8;
@@ -56,14 +58,15 @@ struct GemmArgs {
     unsigned int* status;
 };
 
-DEVINL void epi_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-// barrier over the 128 epilogue threads that also ORs a predicate: every thread gets the same answer
+DEVINL void epi_barrier() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+DEVINL void group_barrier(int grp) { asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory"); }
+// barrier over the 256 epilogue threads that also ORs a predicate: every thread gets the same answer
 DEVINL bool epi_any(int pred) {
     uint32_t r;
     asm volatile(
         "{\n\t.reg .pred p, q;\n\t"
         "setp.ne.u32 q, %1, 0;\n\t"
-        "bar.red.or.pred p, 1, 128, q;\n\t"
+        "bar.red.or.pred p, 1, 256, q;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}" : "=r"(r) : "r"(pred) : "memory");
     return r != 0;
 }
@@ -80,7 +83,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     uint64_t* empty = bars + STAGES;          // [STAGES]
     uint64_t* acc_full = bars + 2 * STAGES;   // [2]
     uint64_t* acc_empty = acc_full + 2;       // [2]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    uint64_t* aux_full = acc_empty + 2;       // [2] one per epilogue group (EPI_DGELU)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aux_full + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     int* last_flag = const_cast<int*>(abort_flag) + 1;
 
@@ -89,14 +93,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        for (int b = 0; b < 2; b++) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+        for (int b = 0; b < 2; b++) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 8); mbar_init(&aux_full[b], 1); }
         *abort_flag = 0;
         mbar_fence_init();
     }
     if (warp == 0 && lane == 0) {
         tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB);
         if (MODE != EPI_ACCUM) tma_prefetch_desc(&tmD);
-        if (MODE == EPI_GELU) tma_prefetch_desc(&tmAux);
+        if (MODE == EPI_GELU || MODE == EPI_DGELU) tma_prefetch_desc(&tmAux);
     }
     if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
     tc_fence_before();
@@ -183,104 +187,112 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             }
         }
     } else {
-        // ---------------- epilogue (warps 2..5) ----------------
+        // ---------------- epilogue (warps 2..9) ----------------
+        // Two groups of four warps; group g owns columns [128 g, 128 g + 128) of the tile and works through them
+        // in 32-column chunks staged in 64-byte-swizzled shared memory (two 8 KB buffers per group).
+        const int ew = warp - 2;
+        const int grp = ew >> 2;
         const int q = warp & 3;                        // TMEM lane quarter this warp may access
         const int row = q * 32 + lane;                 // row of the tile owned by this thread
-        const bool store_thread = (threadIdx.x == 64);
+        const bool leader = ((ew & 3) == 0) && lane == 0;          // issues this group's TMA traffic
+        const bool store_thread = (threadIdx.x == 64);             // ACCUM mode: split-K bookkeeping
+        uint8_t* bufA = epi_smem + (grp * 2 + 0) * EPI_BUF_BYTES;
+        uint8_t* bufB = epi_smem + (grp * 2 + 1) * EPI_BUF_BYTES;
+        constexpr int CHUNKS = (BN / 2) / EPI_COLS;
+        const int swz = (row >> 1) & 3;                // 64-byte swizzle: 16-byte unit j of row r sits at unit j ^ ((r >> 1) & 3)
+        uint8_t* rowA = bufA + row * 64;
+        uint8_t* rowB = bufB + row * 64;
+        uint32_t kctr = 0;
+        auto aux_load = [&](int w_, int c_) {           // pre-activation chunk -> bufB (EPI_DGELU)
+            int mt_, nt_, sp_; decode(w_, mt_, nt_, sp_);
+            mbar_expect_tx(&aux_full[grp], EPI_BUF_BYTES);
+            tma_load_2d(bufB, &tmAux, &aux_full[grp], nt_ * BN + grp * (BN / 2) + c_ * EPI_COLS, mt_ * BM);
+        };
+        if (MODE == EPI_DGELU && leader && (int)blockIdx.x < total_work) aux_load(blockIdx.x, 0);
         int it = 0;
-        uint32_t chunk_ctr = 0;
         for (int w = blockIdx.x; w < total_work; w += gridDim.x, it++) {
             int mt, nt, sp; decode(w, mt, nt, sp);
             const int buf = it & 1;
             const uint32_t use = (uint32_t)(it >> 1);
-            const bool ok = mbar_wait(&acc_full[buf], use & 1, abort_flag, g.status, 0x400 + buf);
+            bool ok = mbar_wait(&acc_full[buf], use & 1, abort_flag, g.status, 0x400 + buf);
             tc_fence_after();
-            const int m0 = mt * BM, n0 = nt * BN;
+            const int m0 = mt * BM, n0 = nt * BN + grp * (BN / 2);
             const int grow = m0 + row;
-            const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
+            const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + grp * (BN / 2);
 
             if (MODE != EPI_ACCUM) {
                 #pragma unroll 1
-                for (int c = 0; c < BN / EPI_COLS; c++) {
+                for (int c = 0; c < CHUNKS; c++) {
                     const int col0 = n0 + c * EPI_COLS;
-                    if (col0 >= g.N) break;           // uniform over the CTA
-                    uint32_t v[64];
+                    uint32_t v[32];
                     tmem_ld32(t_row + c * EPI_COLS, v);
-                    tmem_ld32(t_row + c * EPI_COLS + 32, v + 32);
                     tmem_ld_wait();
                     float* f = reinterpret_cast<float*>(v);
-                    if (MODE == EPI_STORE || MODE == EPI_GELU) {
-                        if (g.bias != nullptr) {
-                            #pragma unroll
-                            for (int j = 0; j < 64; j += 8) {
-                                if (col0 + j < g.N) {   // N is a multiple of 8
-                                    bf16x8 b = ld128(g.bias + col0 + j);
-                                    #pragma unroll
-                                    for (int e = 0; e < 8; e++) f[j + e] += __bfloat162float(b[e]);
-                                }
-                            }
-                        }
-                    }
-                    uint8_t* sbuf0; uint8_t* sbuf1 = nullptr;
-                    if (MODE == EPI_GELU) {
-                        // both staging buffers are used by this chunk: wait for every earlier store to have read them
-                        if (store_thread) tma_store_wait_read<0>();
-                        sbuf0 = epi_smem; sbuf1 = epi_smem + EPI_BUF_BYTES;
-                    } else {
-                        if (store_thread) tma_store_wait_read<1>();
-                        sbuf0 = epi_smem + (chunk_ctr & 1) * EPI_BUF_BYTES;
-                    }
-                    chunk_ctr++;
-                    epi_barrier();
-                    if (MODE == EPI_DGELU) {
-                        const bool rok = grow < g.M;
+                    if ((MODE == EPI_STORE || MODE == EPI_GELU) && g.bias != nullptr) {
                         #pragma unroll
-                        for (int j = 0; j < 64; j += 8) {
-                            if (rok && col0 + j < g.N) {
-                                bf16x8 a = ld128cs(g.aux + (size_t)grow * g.ldd + col0 + j);
+                        for (int j = 0; j < 32; j += 8) {
+                            if (col0 + j < g.N) {   // N is a multiple of 8
+                                bf16x8 b = ld128(g.bias + col0 + j);
                                 #pragma unroll
-                                for (int e = 0; e < 8; e++) f[j + e] *= gelu_tanh_grad(__bfloat162float(a[e]));
+                                for (int e = 0; e < 8; e++) f[j + e] += __bfloat162float(b[e]);
                             }
                         }
                     }
-                    // 128-byte swizzle: 16-byte chunk j of row r lives at chunk position j ^ (r & 7)
-                    uint8_t* srow0 = sbuf0 + row * 128;
-                    if (MODE == EPI_GELU) {
-                        uint8_t* srow1 = sbuf1 + row * 128;
+                    uint8_t* out_row = rowA;
+                    const uint8_t* out_buf = bufA;
+                    if (MODE == EPI_STORE) {
+                        if (kctr & 1) { out_row = rowB; out_buf = bufB; }
+                        if (leader) tma_store_wait_read<1>();      // the store issued two chunks ago has read this buffer
+                    } else {
+                        if (leader) tma_store_wait_read<0>();
+                    }
+                    if (MODE == EPI_DGELU) {
+                        ok = mbar_wait(&aux_full[grp], kctr & 1, abort_flag, g.status, 0x440 + grp) && ok;
                         #pragma unroll
-                        for (int j = 0; j < 8; j++) {
+                        for (int j = 0; j < 4; j++) {
+                            const uint4 a = *reinterpret_cast<const uint4*>(rowB + ((j ^ swz) * 16));
+                            const float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), a2 = unpack_bf16x2(a.z), a3 = unpack_bf16x2(a.w);
+                            f[j*8+0] *= gelu_grad_fast(a0.x); f[j*8+1] *= gelu_grad_fast(a0.y);
+                            f[j*8+2] *= gelu_grad_fast(a1.x); f[j*8+3] *= gelu_grad_fast(a1.y);
+                            f[j*8+4] *= gelu_grad_fast(a2.x); f[j*8+5] *= gelu_grad_fast(a2.y);
+                            f[j*8+6] *= gelu_grad_fast(a3.x); f[j*8+7] *= gelu_grad_fast(a3.y);
+                        }
+                    }
+                    group_barrier(grp);      // output buffer is free; (DGELU) everybody has read the pre-activation chunk
+                    if (MODE == EPI_DGELU && leader) {
+                        if (c + 1 < CHUNKS) aux_load(w, c + 1);
+                        else if (w + (int)gridDim.x < total_work) aux_load(w + gridDim.x, 0);
+                    }
+                    if (MODE == EPI_GELU) {
+                        #pragma unroll
+                        for (int j = 0; j < 4; j++) {
                             uint4 pre, post;
-                            float x0 = f[j*8+0], x1 = f[j*8+1], x2 = f[j*8+2], x3 = f[j*8+3];
-                            float x4 = f[j*8+4], x5 = f[j*8+5], x6 = f[j*8+6], x7 = f[j*8+7];
-                            pre.x = pack_bf16x2(x0, x1); pre.y = pack_bf16x2(x2, x3);
-                            pre.z = pack_bf16x2(x4, x5); pre.w = pack_bf16x2(x6, x7);
-                            // GELU is applied to the bf16-rounded pre-activation so that a later recompute
-                            // from the stored pre-activation reproduces the same values
-                            float2 r0 = unpack_bf16x2(pre.x), r1 = unpack_bf16x2(pre.y), r2 = unpack_bf16x2(pre.z), r3 = unpack_bf16x2(pre.w);
-                            post.x = pack_bf16x2(gelu_tanh(r0.x), gelu_tanh(r0.y));
-                            post.y = pack_bf16x2(gelu_tanh(r1.x), gelu_tanh(r1.y));
-                            post.z = pack_bf16x2(gelu_tanh(r2.x), gelu_tanh(r2.y));
-                            post.w = pack_bf16x2(gelu_tanh(r3.x), gelu_tanh(r3.y));
-                            const int pos = (j ^ (row & 7)) * 16;
-                            *reinterpret_cast<uint4*>(srow1 + pos) = pre;
-                            *reinterpret_cast<uint4*>(srow0 + pos) = post;
+                            pre.x = pack_bf16x2(f[j*8+0], f[j*8+1]); pre.y = pack_bf16x2(f[j*8+2], f[j*8+3]);
+                            pre.z = pack_bf16x2(f[j*8+4], f[j*8+5]); pre.w = pack_bf16x2(f[j*8+6], f[j*8+7]);
+                            // GELU of the bf16-rounded pre-activation: a later recompute from the stored value gives the same bits
+                            const float2 r0 = unpack_bf16x2(pre.x), r1 = unpack_bf16x2(pre.y), r2 = unpack_bf16x2(pre.z), r3 = unpack_bf16x2(pre.w);
+                            post.x = pack_bf16x2(gelu_fast(r0.x), gelu_fast(r0.y)); post.y = pack_bf16x2(gelu_fast(r1.x), gelu_fast(r1.y));
+                            post.z = pack_bf16x2(gelu_fast(r2.x), gelu_fast(r2.y)); post.w = pack_bf16x2(gelu_fast(r3.x), gelu_fast(r3.y));
+                            *reinterpret_cast<uint4*>(rowB + ((j ^ swz) * 16)) = pre;
+                            *reinterpret_cast<uint4*>(rowA + ((j ^ swz) * 16)) = post;
                         }
                     } else {
                         #pragma unroll
-                        for (int j = 0; j < 8; j++) {
+                        for (int j = 0; j < 4; j++) {
                             uint4 o;
                             o.x = pack_bf16x2(f[j*8+0], f[j*8+1]); o.y = pack_bf16x2(f[j*8+2], f[j*8+3]);
                             o.z = pack_bf16x2(f[j*8+4], f[j*8+5]); o.w = pack_bf16x2(f[j*8+6], f[j*8+7]);
-                            *reinterpret_cast<uint4*>(srow0 + ((j ^ (row & 7)) * 16)) = o;
+                            *reinterpret_cast<uint4*>(out_row + ((j ^ swz) * 16)) = o;
                         }
                     }
                     fence_async_smem();
-                    epi_barrier();
-                    if (store_thread && ok) {
-                        tma_store_2d(&tmD, sbuf0, col0, m0);
-                        if (MODE == EPI_GELU) tma_store_2d(&tmAux, sbuf1, col0, m0);
+                    group_barrier(grp);
+                    if (leader && ok && col0 < g.N) {
+                        tma_store_2d(&tmD, out_buf, col0, m0);
+                        if (MODE == EPI_GELU) tma_store_2d(&tmAux, bufB, col0, m0);
                         tma_store_commit();
                     }
+                    kctr++;
                 }
                 // accumulator fully read: hand it back to the MMA warp
                 tc_fence_before();
@@ -291,7 +303,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 const int tile = mt * g.num_n_tiles + nt;
                 if (g.splits == 1) {
                     #pragma unroll 1
-                    for (int c = 0; c < BN / 32; c++) {
+                    for (int c = 0; c < CHUNKS; c++) {
                         const int col0 = n0 + c * 32;
                         if (col0 >= g.N) break;
                         uint32_t v[32];
@@ -323,15 +335,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 } else {
                     // partial tile -> workspace, laid out [col/4][row][4] so that a warp writes 512 contiguous bytes
                     float* wsp = g.workspace + ((size_t)tile * g.splits + sp) * (BM * BN);
+                    const int cbase = grp * (BN / 2);
                     #pragma unroll 1
-                    for (int c = 0; c < BN / 32; c++) {
+                    for (int c = 0; c < CHUNKS; c++) {
                         uint32_t v[32];
                         tmem_ld32(t_row + c * 32, v);
                         tmem_ld_wait();
                         #pragma unroll
                         for (int j = 0; j < 32; j += 4) {
                             float4 o = make_float4(__uint_as_float(v[j]), __uint_as_float(v[j+1]), __uint_as_float(v[j+2]), __uint_as_float(v[j+3]));
-                            __stcg(reinterpret_cast<float4*>(wsp + ((size_t)((c * 32 + j) >> 2) * BM + row) * 4), o);
+                            __stcg(reinterpret_cast<float4*>(wsp + ((size_t)((cbase + c * 32 + j) >> 2) * BM + row) * 4), o);
                         }
                     }
                     tc_fence_before();
@@ -350,8 +363,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                         const float* wt = g.workspace + (size_t)tile * g.splits * (BM * BN);
                         if (grow < g.M) {
                             #pragma unroll 1
-                            for (int j = 0; j < BN; j += 8) {
-                                if (n0 + j >= g.N) break;
+                            for (int jj = 0; jj < BN / 2; jj += 8) {
+                                const int j = cbase + jj;              // column inside the tile
+                                if (nt * BN + j >= g.N) break;
                                 float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
                                 // all loads of a group of splits are issued before the adds (memory-level parallelism);
                                 // the adds run in split order: deterministic
@@ -373,7 +387,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                                         }
                                     }
                                 }
-                                bf16* dp = g.D + (size_t)grow * g.ldd + n0 + j;
+                                bf16* dp = g.D + (size_t)grow * g.ldd + nt * BN + j;
                                 bf16x8 o;
                                 if (g.accumulate) {
                                     bf16x8 old = ld128(dp);
@@ -392,7 +406,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             }
             if (epi_any(*abort_flag)) break;   // uniform decision: nobody is left alone at a barrier
         }
-        if (store_thread) tma_store_wait<0>();
+        if (leader) tma_store_wait<0>();
     }
 
     // teardown: everybody meets, then the allocating warp frees TMEM
@@ -493,9 +507,9 @@ extern "C" int llmc_gemm(const bf16* A, const bf16* B, bf16* D, const bf16* bias
     {
         uint64_t dims[2] = {(uint64_t)N, (uint64_t)M}, strides[2] = {2, (uint64_t)ldd * 2};
         uint32_t box[2] = {EPI_COLS, BM};
-        if ((rc = llmc_get_tensormap(&tmD, D, 2, 2, dims, strides, box, 3))) return rc;
+        if ((rc = llmc_get_tensormap(&tmD, D, 2, 2, dims, strides, box, 2))) return rc;       // 64-byte swizzle
         tmAux = tmD;
-        if (mode == EPI_GELU) { if ((rc = llmc_get_tensormap(&tmAux, aux, 2, 2, dims, strides, box, 3))) return rc; }
+        if (mode == EPI_GELU || mode == EPI_DGELU) { if ((rc = llmc_get_tensormap(&tmAux, aux, 2, 2, dims, strides, box, 2))) return rc; }
     }
     int sms = llmc_device_sm_count();
     if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;

@@ -1,0 +1,47 @@
+"""Host-side logic of data parallelism and ZeRO-1 on CPU ranks (gloo): sharding rule, gradient averaging, sharded
+AdamW and parameter all-gather must reproduce the single-process run with gradient accumulation.  Also the failure
+path: a rank that raises must make the job fail promptly instead of hanging (failures are injected on the host only)."""
+import os
+import subprocess
+import sys
+import time
+
+import pytest
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+WORKER = os.path.join(HERE, "dist_worker.py")
+
+
+def launch(world, out, extra, port, timeout=300):
+    env = dict(os.environ, OMP_NUM_THREADS="2")
+    if world == 1:
+        cmd = [sys.executable, WORKER, "--out", out] + extra
+    else:
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world), "--master-addr", "127.0.0.1",
+               "--master-port", str(port), WORKER, "--out", out] + extra
+    return subprocess.run(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=timeout)
+
+
+@pytest.mark.parametrize("zero", [0, 1])
+def test_two_ranks_match_single_process(tmp_path, zero):
+    single, multi = str(tmp_path / "single.pt"), str(tmp_path / "multi.pt")
+    r1 = launch(1, single, ["--device", "cpu", "--zero", "0", "--slots", "2"], 0)
+    assert r1.returncode == 0, r1.stdout[-2000:]
+    r2 = launch(2, multi, ["--device", "cpu", "--zero", str(zero), "--slots", "2"], 29511 + zero)
+    assert r2.returncode == 0, r2.stdout[-2000:]
+    a, b = torch.load(single), torch.load(multi)
+    assert b["zero"] == zero
+    assert max(abs(x - y) for x, y in zip(a["losses"], b["losses"])) < 1e-4
+    assert torch.allclose(a["params"], b["params"], atol=2e-5, rtol=1e-4)
+    assert a["losses"][-1] < a["losses"][0]
+
+
+def test_rank_failure_ends_the_job_without_hanging(tmp_path):
+    out = str(tmp_path / "never.pt")
+    t0 = time.time()
+    r = launch(2, out, ["--device", "cpu", "--zero", "1", "--slots", "2", "--fail-rank", "1"], 29531, timeout=240)
+    assert r.returncode != 0
+    assert "injected failure" in r.stdout
+    assert time.time() - t0 < 200
+    assert not os.path.exists(out)
