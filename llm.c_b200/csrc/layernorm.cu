@@ -1,8 +1,7 @@
 // LayerNorm forward, fused residual-add + LayerNorm forward, and LayerNorm backward for bf16
 // activations with fp32 statistics.
 //
-// Forward: one warp per row, 128-bit loads, the row stays in registers between the mean/variance
-// passes and the normalise pass (rows up to 8192 channels; wider rows re-read through L1).
+// Forward: one warp per row, 128-bit loads; the second and third pass over the row hit L1.
 // Backward: each CTA walks a contiguous strip of rows; every lane keeps the dweight/dbias partial
 // sums of "its" channels in registers across the strip, the CTA folds its warps in a fixed order
 // and writes one fp32 partial row per CTA; a second tiny kernel folds the CTA partials in CTA order
@@ -14,8 +13,10 @@
 
 namespace {
 
-constexpr int MAXP = 4;   // packs (of 8 channels) per lane held in registers => rows up to 32*8*MAXP = 1024 per "slab"
-// Rows wider than a slab are processed slab by slab.
+// Backward: MAXP packs (of 8 channels) per lane are held in registers => 32*8*MAXP channels per "slab"
+// (MAXP = 3 covers C <= 768 with fewer registers, MAXP = 4 everything else; rows wider than a slab go slab by slab).
+constexpr int LNB_WARPS = 4;         // warps per CTA of the backward kernel
+constexpr int LNB_CTAS_PER_SM = 4;
 
 template <bool FUSED_RESIDUAL>
 __global__ void __launch_bounds__(256)
@@ -76,8 +77,8 @@ ln_fwd_kernel(bf16* __restrict__ out, float* __restrict__ mean_out, float* __res
 }
 
 // dinp (+)= LN'(dout); per-CTA fp32 partials of dweight/dbias -> partials[cta][2][C]
-template <bool ACCUM_DINP>
-__global__ void __launch_bounds__(256)
+template <bool ACCUM_DINP, int MAXP>
+__global__ void __launch_bounds__(LNB_WARPS * 32, LNB_CTAS_PER_SM)
 ln_bwd_kernel(bf16* __restrict__ dinp, float* __restrict__ partials, const bf16* __restrict__ dout,
               const bf16* __restrict__ inp, const bf16* __restrict__ weight,
               const float* __restrict__ mean, const float* __restrict__ rstd, int N, int C, int rows_per_cta) {
@@ -96,19 +97,42 @@ ln_bwd_kernel(bf16* __restrict__ dinp, float* __restrict__ partials, const bf16*
             #pragma unroll
             for (int e = 0; e < 8; e++) { dw[i][e] = 0.f; db[i][e] = 0.f; }
 
+        const bool single_slab = npack <= slab_packs;
         for (int row = row0 + warp; row < row1; row += nwarps) {
             const bf16* dy = dout + (size_t)row * C;
             const bf16* x = inp + (size_t)row * C;
             const float m = mean[row], rs = rstd[row];
-            // row-wide sums (needed for every slab)
+            // row-wide sums (needed for every slab); a row that fits one slab is kept in registers for the second pass
+            bf16x8 cd[MAXP], cx[MAXP];
             float s1 = 0.f, s2 = 0.f;
-            for (int p = lane; p < npack; p += 32) {
-                bf16x8 d = ld128(dy + p * 8), a = ld128(x + p * 8), w = ld128(weight + p * 8);
+            if (single_slab) {
                 #pragma unroll
-                for (int e = 0; e < 8; e++) {
-                    float dn = __bfloat162float(d[e]) * __bfloat162float(w[e]);
-                    float nn = (__bfloat162float(a[e]) - m) * rs;
-                    s1 += dn; s2 += dn * nn;
+                for (int i = 0; i < MAXP; i++) {
+                    const int p = lane + 32 * i;
+                    if (p < npack) { cd[i] = ld128cs(dy + p * 8); cx[i] = ld128cs(x + p * 8); }
+                }
+                #pragma unroll
+                for (int i = 0; i < MAXP; i++) {
+                    const int p = lane + 32 * i;
+                    if (p < npack) {
+                        bf16x8 w = ld128(weight + p * 8);
+                        #pragma unroll
+                        for (int e = 0; e < 8; e++) {
+                            float dn = __bfloat162float(cd[i][e]) * __bfloat162float(w[e]);
+                            float nn = (__bfloat162float(cx[i][e]) - m) * rs;
+                            s1 += dn; s2 += dn * nn;
+                        }
+                    }
+                }
+            } else {
+                for (int p = lane; p < npack; p += 32) {
+                    bf16x8 d = ld128(dy + p * 8), a = ld128(x + p * 8), w = ld128(weight + p * 8);
+                    #pragma unroll
+                    for (int e = 0; e < 8; e++) {
+                        float dn = __bfloat162float(d[e]) * __bfloat162float(w[e]);
+                        float nn = (__bfloat162float(a[e]) - m) * rs;
+                        s1 += dn; s2 += dn * nn;
+                    }
                 }
             }
             s1 = warp_sum(s1) / C; s2 = warp_sum(s2) / C;
@@ -117,7 +141,9 @@ ln_bwd_kernel(bf16* __restrict__ dinp, float* __restrict__ partials, const bf16*
             for (int i = 0; i < MAXP; i++) {
                 const int p = slab0 + lane + 32 * i;
                 if (p < npack) {
-                    bf16x8 d = ld128(dy + p * 8), a = ld128(x + p * 8), w = ld128(weight + p * 8);
+                    bf16x8 d, a;
+                    if (single_slab) { d = cd[i]; a = cx[i]; } else { d = ld128(dy + p * 8); a = ld128(x + p * 8); }
+                    bf16x8 w = ld128(weight + p * 8);
                     bf16x8 o;
                     if (ACCUM_DINP) o = ld128(dx + p * 8);
                     #pragma unroll
@@ -198,7 +224,7 @@ extern "C" int llmc_fused_residual_fwd(bf16* residual, bf16* normed, float* mean
 // Number of fp32 scratch elements llmc_layernorm_bwd needs
 extern "C" long long llmc_layernorm_bwd_scratch(int N, int C) {
     int sms = llmc_device_sm_count(); if (sms <= 0) sms = 148;
-    return (long long)(2 * sms) * 2 * C;
+    return (long long)(LNB_CTAS_PER_SM * sms) * 2 * C;
 }
 
 // dinp (+)= dLN ; dweight, dbias (+)= column sums.  `scratch` holds llmc_layernorm_bwd_scratch floats.
@@ -207,19 +233,24 @@ extern "C" int llmc_layernorm_bwd(bf16* dinp, bf16* dweight, bf16* dbias, float*
                                   int accumulate_dinp, int accumulate_dwdb, cudaStream_t stream) {
     if (C % 8) return -1;
     int sms = llmc_device_sm_count(); if (sms <= 0) sms = 148;
-    int ctas = 2 * sms;
+    int ctas = LNB_CTAS_PER_SM * sms;
     int rows_per_cta = CEIL_DIV(N, ctas);
     ctas = CEIL_DIV(N, rows_per_cta);
-    const int nwarps = 8;
-    size_t smem = (size_t)nwarps * 2 * (32 * MAXP * 8) * sizeof(float);   // 64 KB
+    const int nwarps = LNB_WARPS;
+    const int maxp = (C <= 768) ? 3 : 4;
+    size_t smem = (size_t)nwarps * 2 * (32 * maxp * 8) * sizeof(float);
     static bool configured = false;
     if (!configured) {
-        CUDA_CHECK(cudaFuncSetAttribute(ln_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        CUDA_CHECK(cudaFuncSetAttribute(ln_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        const int big = (int)((size_t)nwarps * 2 * (32 * 4 * 8) * sizeof(float));
+        CUDA_CHECK(cudaFuncSetAttribute(ln_bwd_kernel<true, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+        CUDA_CHECK(cudaFuncSetAttribute(ln_bwd_kernel<false, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+        CUDA_CHECK(cudaFuncSetAttribute(ln_bwd_kernel<true, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
+        CUDA_CHECK(cudaFuncSetAttribute(ln_bwd_kernel<false, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, big));
         configured = true;
     }
-    if (accumulate_dinp) ln_bwd_kernel<true><<<ctas, nwarps * 32, smem, stream>>>(dinp, scratch, dout, inp, weight, mean, rstd, N, C, rows_per_cta);
-    else ln_bwd_kernel<false><<<ctas, nwarps * 32, smem, stream>>>(dinp, scratch, dout, inp, weight, mean, rstd, N, C, rows_per_cta);
+    auto kfn = accumulate_dinp ? (maxp == 3 ? ln_bwd_kernel<true, 3> : ln_bwd_kernel<true, 4>)
+                               : (maxp == 3 ? ln_bwd_kernel<false, 3> : ln_bwd_kernel<false, 4>);
+    kfn<<<ctas, nwarps * 32, smem, stream>>>(dinp, scratch, dout, inp, weight, mean, rstd, N, C, rows_per_cta);
     CUDA_CHECK(cudaGetLastError());
     ln_bwd_fold_kernel<<<CEIL_DIV(C, 128), 128, 0, stream>>>(dweight, dbias, scratch, ctas, C, accumulate_dwdb);
     CUDA_CHECK(cudaGetLastError());
