@@ -56,6 +56,9 @@ constexpr int SIG_BARRIER = 201 * MAX_RANKS;
 constexpr int SIG_SCALAR = 202 * MAX_RANKS;     // [parity][src rank] packed {seq, float}
 constexpr int SIG_WORDS = 208 * MAX_RANKS;
 
+// limit of every peer-flag wait in clock cycles; adjustable at run time (tests shorten it)
+__device__ long long g_flag_wait_cycles = FLAG_WAIT_CYCLES;
+
 namespace {
 
 DEVINL void st_release_sys(unsigned long long* p, unsigned long long v) {
@@ -70,7 +73,7 @@ DEVINL unsigned long long ld_acquire_sys(const unsigned long long* p) {
 DEVINL bool wait_flag_ge(const unsigned long long* p, unsigned long long want, unsigned int* status, unsigned int where) {
     long long t0 = clock64();
     while (ld_acquire_sys(p) < want) {
-        if (clock64() - t0 > FLAG_WAIT_CYCLES) { record_error(status, ST_FLAG_TIMEOUT, where); return false; }
+        if (clock64() - t0 > g_flag_wait_cycles) { record_error(status, ST_FLAG_TIMEOUT, where); return false; }
         __nanosleep(200);
     }
     return true;
@@ -147,7 +150,7 @@ __global__ void scalar_allreduce_kernel(PeerPtrs sig, float* __restrict__ inout,
         long long t0 = clock64();
         unsigned long long w;
         while (((w = ld_acquire_sys(slot)) >> 32) < (seq & 0xFFFFFFFFull)) {
-            if (clock64() - t0 > FLAG_WAIT_CYCLES) { record_error(status, ST_FLAG_TIMEOUT, 0x720 + threadIdx.x); ok_s = 0; break; }
+            if (clock64() - t0 > g_flag_wait_cycles) { record_error(status, ST_FLAG_TIMEOUT, 0x720 + threadIdx.x); ok_s = 0; break; }
             __nanosleep(100);
         }
         vals[threadIdx.x] = __uint_as_float((unsigned int)(w & 0xFFFFFFFFull));
@@ -257,6 +260,13 @@ int fill(PeerPtrs* pp, const unsigned long long* ptrs, int N) {
 }  // namespace
 
 extern "C" int llmc_p2p_signal_words() { return SIG_WORDS; }
+
+// Sets the limit (clock cycles) after which a wait on a peer flag gives up and records ST_FLAG_TIMEOUT. 0 restores the default.
+extern "C" int llmc_p2p_set_wait_cycles(long long cycles) {
+    long long v = cycles > 0 ? cycles : FLAG_WAIT_CYCLES;
+    CUDA_CHECK(cudaMemcpyToSymbol(g_flag_wait_cycles, &v, sizeof(v)));
+    return 0;
+}
 
 // Reduce-scatter (mean) of up to 16 slices of the gradient buffers. grad_ptrs / sig_ptrs: N device pointers (one per rank).
 // Every slice size must be a multiple of 8*N. norm_partials: `ctas` floats (may be null).

@@ -48,6 +48,7 @@ Options (same letters as the reference trainer):
   -z <int> ZeRO stage 0|1 (0)   -r <int> recompute 0|1|2 (1)
   -pn <int> num processes  -pr <int> process rank  -pg <int> GPUs per node  -pi <str> init method mpi|tcp|fs  -ps <ip>  -pf <path>
 Extensions:  -dev cpu|cuda   -dt bf16|fp32   -cb nccl|p2p (communication backend of the multi-GPU step)
+             -b2 <float> AdamW beta2 (0.95)   -gc <float> gradient clipping norm (1.0; 0 = off)   -hp / -tp HellaSwag / tokenizer paths
 """
 
 
@@ -97,6 +98,8 @@ class TrainConfig:
     tokenizer_path: str = "gpt2_tokenizer.bin"
     quiet: bool = False
     prefetch: bool = True
+    beta2: float = 0.95
+    grad_clip: float = 1.0
 
 
 _FLAGS = {
@@ -111,7 +114,7 @@ _FLAGS = {
     "-pr": ("process_rank", int), "-pg": ("gpus_per_node", int), "-pi": ("nccl_init_method", str), "-pm": ("nccl_init_method", str),
     "-ps": ("server_ip", str), "-pf": ("fs_path", str), "-pp": ("fs_path", str), "-sl": ("skip_update_lossz", float),
     "-sg": ("skip_update_gradz", float), "-dev": ("device", str), "-dt": ("dtype", str), "-cb": ("comm_backend", str),
-    "-hp": ("hellaswag_path", str), "-tp": ("tokenizer_path", str),
+    "-hp": ("hellaswag_path", str), "-tp": ("tokenizer_path", str), "-b2": ("beta2", float), "-gc": ("grad_clip", float),
 }
 
 
@@ -209,7 +212,8 @@ class Trainer:
         if arena is not None:
             from .parallel import p2p
             backend = p2p.P2PBackend(m, d, arena, sym_bufs["params"], sym_bufs["grads"])
-        self.opt = ShardedAdamW(m, d, c.zero_stage, bool(c.use_master_weights), backend)
+        self.opt = ShardedAdamW(m, d, c.zero_stage, bool(c.use_master_weights), backend, beta2=c.beta2,
+                                grad_clip=(c.grad_clip if c.grad_clip > 0 else 1e30))
         self.logger = Logger(c.output_log_dir, d.process_rank, self.resuming)
         self.tokenizer = Tokenizer(c.tokenizer_path)
         self.scheduler = LearningRateScheduler(c.lr_scheduler_type, c.learning_rate, c.warmup_iterations, self.train_num_batches,
