@@ -51,7 +51,7 @@ def cuda():
         "llmc_fused_residual_fwd": (I, [P, P, P, P, P, P, P, P, I, I, S]),
         "llmc_layernorm_bwd_scratch": (L, [I, I]),
         "llmc_layernorm_bwd": (I, [P, P, P, P, P, P, P, P, P, I, I, I, I, S]),
-        "llmc_encoder_fwd": (I, [P, P, P, P, I, I, I, S]),
+        "llmc_encoder_fwd": (I, [P, P, P, P, I, I, I, I, S]),
         "llmc_encoder_bwd": (I, [P, P, P, P, I, I, I, I, I, I, U, S]),
         "llmc_fused_classifier": (I, [P, P, P, F, I, I, I, I, I, S]),
         "llmc_gelu_fwd": (I, [P, P, L, S]),

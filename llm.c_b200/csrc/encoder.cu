@@ -14,14 +14,14 @@
 namespace {
 
 __global__ void encoder_fwd_kernel(bf16* __restrict__ out, const int* __restrict__ tokens, const bf16* __restrict__ wte,
-                                   const bf16* __restrict__ wpe, int B, int T, int C) {
+                                   const bf16* __restrict__ wpe, int B, int T, int C, int V) {
     const int cp = C >> 3;
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (long long)B * T * cp) return;
     const int p = (int)(idx % cp);
     const long long bt = idx / cp;
     const int t = (int)(bt % T);
-    const int tok = tokens[bt];
+    const int tok = min(max(tokens[bt], 0), V - 1);      // ids are validated on the host; never index outside the table
     bf16x8 a = ld128(wte + (size_t)tok * C + p * 8);
     bf16x8 b = ld128(wpe + (size_t)t * C + p * 8);
     bf16x8 o;
@@ -169,10 +169,10 @@ wte_bwd_kernel(bf16* __restrict__ dwte, const bf16* __restrict__ dout, const int
 
 }  // namespace
 
-extern "C" int llmc_encoder_fwd(bf16* out, const int* tokens, const bf16* wte, const bf16* wpe, int B, int T, int C, cudaStream_t stream) {
+extern "C" int llmc_encoder_fwd(bf16* out, const int* tokens, const bf16* wte, const bf16* wpe, int B, int T, int C, int V, cudaStream_t stream) {
     if (C % 8) return -1;
     long long total = (long long)B * T * (C / 8);
-    encoder_fwd_kernel<<<(unsigned)CEIL_DIV(total, 256), 256, 0, stream>>>(out, tokens, wte, wpe, B, T, C);
+    encoder_fwd_kernel<<<(unsigned)CEIL_DIV(total, 256), 256, 0, stream>>>(out, tokens, wte, wpe, B, T, C, V);
     CUDA_CHECK(cudaGetLastError());
     return 0;
 }

@@ -106,7 +106,7 @@ def encoder_forward(out, tokens, wte, wpe):
     B, T = tokens.shape
     C = wte.shape[1]
     _launches += 1
-    check(_lib.cuda().llmc_encoder_fwd(_p(out), _p(tokens), _p(wte), _p(wpe), B, T, C, _stream()), "llmc_encoder_fwd")
+    check(_lib.cuda().llmc_encoder_fwd(_p(out), _p(tokens), _p(wte), _p(wpe), B, T, C, wte.shape[0], _stream()), "llmc_encoder_fwd")
 
 
 def encoder_backward(dwte, dwpe, dout, tokens, accumulate_wte=True, accumulate_wpe=True, seed=0):

@@ -298,6 +298,11 @@ class Trainer:
     # ------------------------------------------------------------------ evaluation helpers
     def _upload(self, inputs, targets, buf_index=None):
         m = self.model
+        # token ids index the embedding table on the device: refuse a corrupt batch on the host (reference: tokenCheck)
+        hi = max(int(inputs.max()), int(targets.max()))
+        lo = min(int(inputs.min()), int(targets.min()))
+        if lo < 0 or hi >= m.cfg.vocab_size:
+            raise ValueError("token id out of range [0, %d): got %d / %d" % (m.cfg.vocab_size, lo, hi))
         m.inputs.copy_(inputs, non_blocking=True)
         m.targets.copy_(targets, non_blocking=True)
         if self._h2d_events is not None and buf_index is not None:
@@ -337,7 +342,7 @@ class Trainer:
             sm.params_flat, sm.params = m.params_flat, m.params
             self._sample_model = sm
         sm = self._sample_model
-        eot = self.tokenizer.eot_token
+        eot = min(self.tokenizer.eot_token, m.cfg.vocab_size - 1)
         Tmax = min(m.cfg.max_seq_len, max(genT, 1))
         chunk = min(self.cfg.T, 256)
         tokens = torch.full((1, Tmax), eot, dtype=torch.int32)
