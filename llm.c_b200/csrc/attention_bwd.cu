@@ -1,4 +1,5 @@
-// Causal flash attention backward for sm_100a on the packed (B, T, 3, NH, HS) layout, HS = 64.
+// Causal flash attention backward for sm_100a on the packed (B, T, 3, NH, HS) layout; head sizes 64..128
+// (multiples of 8; sizes above 64 run as a 128-wide head whose missing channels TMA fills with zeros).
 //
 // Deterministic by construction: no atomics, every output element has one writer and a fixed
 // summation order.  Three launches:
@@ -21,44 +22,53 @@
 // Capability parity: attention_backward_cudnn (llmc/cudnn_att.cpp:256-288) and attention_backward
 // of llmc/attention.cuh in the reference.
 #include "common.cuh"
-#include <stdlib.h>
 
 int llmc_attn_qkv_map(CUtensorMap* tm, const bf16* qkv, int B, int T, int NH, int hs);   // attention_fwd.cu
 
 namespace {
 
-constexpr int HS = 64;
 constexpr int BT = 128;                             // tile rows (queries and keys)
-constexpr int TILE_BYTES = BT * HS * 2;             // 16 KB
-constexpr int PAIR_BYTES = 2 * TILE_BYTES;          // 32 KB
+constexpr int CHUNK_BYTES = 128 * 64 * 2;           // 16 KB: 128 rows x 64 channels, one 128-byte-swizzled TMA box
 constexpr int PS_BYTES = BT * BT * 2;               // 32 KB
-constexpr int XSTAGES = 3;                          // ring of streamed tile pairs
-constexpr int BWD_SMEM = 2 * PAIR_BYTES /*resident, double buffered*/ + XSTAGES * PAIR_BYTES /*stream*/ + 2 * PS_BYTES /*P, dS*/ + 256;
-constexpr int BWD_THREADS = 576;                   // TMA warp + MMA warp + 16 softmax warps
+constexpr int BWD_THREADS = 576;                    // TMA warp + MMA warp + 16 softmax warps
 constexpr int BWD_TMEM_COLS = 512;
+
+// NC = number of 64-channel chunks of the (zero-padded) head: 1 -> head size 64, 2 -> head sizes 72..128.
+// With two chunks a tile pair is 64 KB and an accumulator pair fills the rest of TMEM, so that variant runs without
+// double buffering (one resident buffer, one stream stage, one accumulator set).
+template <int NC> struct BwdCfg {
+    static constexpr int HSP = 64 * NC;
+    static constexpr int TILE_BYTES = NC * CHUNK_BYTES;
+    static constexpr int PAIR_BYTES = 2 * TILE_BYTES;
+    static constexpr int RB = NC == 1 ? 2 : 1;          // resident pair buffers
+    static constexpr int XSTAGES = NC == 1 ? 3 : 1;     // ring of streamed tile pairs
+    static constexpr int ACCBUF = NC == 1 ? 2 : 1;      // TMEM accumulator sets (each 2 * HSP columns)
+    static constexpr int SMEM = RB * PAIR_BYTES + XSTAGES * PAIR_BYTES + 2 * PS_BYTES + 256;
+};
 
 struct BwdArgs {
     bf16* dqkv;          // (B, T, 3, NH, HS)
     const float* lse;    // (B, NH, T)
     const float* delta;  // (B, NH, T)
-    int B, T, NH;
+    int B, T, NH, hs;
     float scale, scale_log2e;
     unsigned int* status;
-    int dbg;             // timing experiments only (LLMC_ATTN_DBG): 1 skip exp, 2 skip accumulate MMAs, 4 skip P/dS stores, 8 skip S/dP MMAs
 };
 
 __global__ void delta_kernel(float* __restrict__ delta, const bf16* __restrict__ out, const bf16* __restrict__ dout,
-                             int B, int T, int NH) {
-    // 8 lanes per (b, t, h) row of 64 channels
+                             int B, int T, int NH, int hs) {
+    // 8 lanes per (b, t, h) row of hs channels
     const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long row = gid >> 3;
     const int part = (int)(gid & 7);
     const long long rows = (long long)B * T * NH;
     float acc = 0.f;
     if (row < rows) {
-        bf16x8 o = ld128cs(out + row * HS + part * 8), d = ld128cs(dout + row * HS + part * 8);
-        #pragma unroll
-        for (int e = 0; e < 8; e++) acc += __bfloat162float(o[e]) * __bfloat162float(d[e]);
+        for (int p = part; p < (hs >> 3); p += 8) {
+            bf16x8 o = ld128cs(out + row * hs + p * 8), d = ld128cs(dout + row * hs + p * 8);
+            #pragma unroll
+            for (int e = 0; e < 8; e++) acc += __bfloat162float(o[e]) * __bfloat162float(d[e]);
+        }
     }
     acc += __shfl_xor_sync(0xffffffffu, acc, 1);
     acc += __shfl_xor_sync(0xffffffffu, acc, 2);
@@ -75,12 +85,15 @@ __global__ void delta_kernel(float* __restrict__ delta, const bf16* __restrict__
 // Persistent: gridDim.x CTAs (one per SM) take work items w = blockIdx.x, blockIdx.x + gridDim.x, ...; the item list is
 // ordered heavy first.  The resident pair and the TMEM accumulators are double buffered so that the loads and the first
 // MMAs of the next item run underneath the epilogue of the current one.
-template <bool DKV>
+template <bool DKV, int NC>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant__ CUtensorMap tmDO, const BwdArgs a) {
+    using Cfg = BwdCfg<NC>;
+    constexpr int HSP = Cfg::HSP, TILE_BYTES = Cfg::TILE_BYTES, PAIR_BYTES = Cfg::PAIR_BYTES;
+    constexpr int RB = Cfg::RB, XSTAGES = Cfg::XSTAGES, ACCBUF = Cfg::ACCBUF;
     extern __shared__ __align__(1024) uint8_t smem[];
-    uint8_t* sRes = smem;                              // [2 buffers][2][16 KB]
-    uint8_t* sStr = sRes + 2 * PAIR_BYTES;             // [XSTAGES][2][16 KB]
+    uint8_t* sRes = smem;                              // [RB][2 tiles]
+    uint8_t* sStr = sRes + RB * PAIR_BYTES;            // [XSTAGES][2 tiles]
     uint8_t* sP = sStr + XSTAGES * PAIR_BYTES;
     uint8_t* sdS = sP + PS_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(sdS + PS_BYTES);
@@ -127,7 +140,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tS = tmem_base, tdP = tmem_base + 128, tAcc = tmem_base + 256;     // two accumulator buffers of 128 columns
+    const uint32_t tS = tmem_base, tdP = tmem_base + 128, tAcc = tmem_base + 256;     // ACCBUF accumulator sets of 2 * HSP columns
+
+    // one 128-row tile = NC boxes of 64 channels
+    auto load_tile = [&](uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, int slot, int row0, int b) {
+        #pragma unroll
+        for (int c = 0; c < NC; c++) tma_load_4d(dst + c * CHUNK_BYTES, tm, bar, c * 64, slot, row0, b);
+    };
 
     if (warp == 0) {
         if (lane == 0) {
@@ -135,16 +154,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
             int it = 0;
             for (int w = blockIdx.x; w < total; w += gridDim.x, it++) {
                 int fixed, b, h, cnt; decode(w, fixed, b, h, cnt);
-                const int rb = it & 1;
-                if (!mbar_wait(&res_empty[rb], ((it >> 1) & 1) ^ 1, abort_flag, a.status, 0x601)) break;
+                const int rb = it % RB;
+                if (!mbar_wait(&res_empty[rb], ((it / RB) & 1) ^ 1, abort_flag, a.status, 0x601)) break;
                 uint8_t* rdst = sRes + rb * PAIR_BYTES;
                 mbar_expect_tx(&res_full[rb], PAIR_BYTES);
                 if (DKV) {
-                    tma_load_4d(rdst, &tmQKV, &res_full[rb], 0, a.NH + h, fixed * BT, b);                   // K_j
-                    tma_load_4d(rdst + TILE_BYTES, &tmQKV, &res_full[rb], 0, 2 * a.NH + h, fixed * BT, b);  // V_j
+                    load_tile(rdst, &tmQKV, &res_full[rb], a.NH + h, fixed * BT, b);                   // K_j
+                    load_tile(rdst + TILE_BYTES, &tmQKV, &res_full[rb], 2 * a.NH + h, fixed * BT, b);  // V_j
                 } else {
-                    tma_load_4d(rdst, &tmQKV, &res_full[rb], 0, h, fixed * BT, b);                          // Q_i
-                    tma_load_4d(rdst + TILE_BYTES, &tmDO, &res_full[rb], 0, h, fixed * BT, b);              // dO_i
+                    load_tile(rdst, &tmQKV, &res_full[rb], h, fixed * BT, b);                          // Q_i
+                    load_tile(rdst + TILE_BYTES, &tmDO, &res_full[rb], h, fixed * BT, b);              // dO_i
                 }
                 bool fail = false;
                 for (int n = 0; n < cnt; n++) {
@@ -152,15 +171,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
                     if (!mbar_wait(&x_empty[st], xph ^ 1, abort_flag, a.status, 0x600)) { fail = true; break; }
                     if (++xst == XSTAGES) { xst = 0; xph ^= 1; }
                     uint8_t* dst = sStr + st * PAIR_BYTES;
-                    if (a.dbg & 64) { mbar_arrive(&x_full[st]); continue; }
                     mbar_expect_tx(&x_full[st], PAIR_BYTES);
                     if (DKV) {
                         const int i = fixed + n;
-                        tma_load_4d(dst, &tmQKV, &x_full[st], 0, h, i * BT, b);                        // Q_i
-                        tma_load_4d(dst + TILE_BYTES, &tmDO, &x_full[st], 0, h, i * BT, b);            // dO_i
+                        load_tile(dst, &tmQKV, &x_full[st], h, i * BT, b);                        // Q_i
+                        load_tile(dst + TILE_BYTES, &tmDO, &x_full[st], h, i * BT, b);            // dO_i
                     } else {
-                        tma_load_4d(dst, &tmQKV, &x_full[st], 0, a.NH + h, n * BT, b);                 // K_j
-                        tma_load_4d(dst + TILE_BYTES, &tmQKV, &x_full[st], 0, 2 * a.NH + h, n * BT, b);// V_j
+                        load_tile(dst, &tmQKV, &x_full[st], a.NH + h, n * BT, b);                 // K_j
+                        load_tile(dst + TILE_BYTES, &tmQKV, &x_full[st], 2 * a.NH + h, n * BT, b);// V_j
                     }
                 }
                 if (fail) break;
@@ -169,21 +187,22 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc_s = umma_idesc_bf16(BT, BT, 0, 0);
-            constexpr uint32_t idesc_acc = DKV ? umma_idesc_bf16(BT, HS, 1, 1) : umma_idesc_bf16(BT, HS, 0, 1);
+            constexpr uint32_t idesc_acc = DKV ? umma_idesc_bf16(BT, HSP, 1, 1) : umma_idesc_bf16(BT, HSP, 0, 1);
             // S = Q K^T and dP = dO V^T of streamed tile t (stage t & 1) against resident buffer rb
             auto issue_sdp = [&](int st, int rb, bool last_of_item) {
                 const uint32_t xs = smem_u32(sStr + st * PAIR_BYTES), rs = smem_u32(sRes + rb * PAIR_BYTES);
                 const uint32_t q = DKV ? xs : rs, dO = (DKV ? xs : rs) + TILE_BYTES;
                 const uint32_t k = DKV ? rs : xs, v = (DKV ? rs : xs) + TILE_BYTES;
-                if (!(a.dbg & 8)) {
                 #pragma unroll
-                for (int kk = 0; kk < HS / 16; kk++)
-                    umma_ss(tS, umma_desc_sw128(q + kk * 32, 16, 1024), umma_desc_sw128(k + kk * 32, 16, 1024), idesc_s, kk > 0);
+                for (int kk = 0; kk < HSP / 16; kk++) {      // 64-channel chunks are 16 KB apart, 16 channels = 32 bytes inside a chunk
+                    const uint32_t off = (kk >> 2) * CHUNK_BYTES + (kk & 3) * 32;
+                    umma_ss(tS, umma_desc_sw128(q + off, 16, 1024), umma_desc_sw128(k + off, 16, 1024), idesc_s, kk > 0);
                 }
-                if (!(a.dbg & 8))
                 #pragma unroll
-                for (int kk = 0; kk < HS / 16; kk++)
-                    umma_ss(tdP, umma_desc_sw128(dO + kk * 32, 16, 1024), umma_desc_sw128(v + kk * 32, 16, 1024), idesc_s, kk > 0);
+                for (int kk = 0; kk < HSP / 16; kk++) {
+                    const uint32_t off = (kk >> 2) * CHUNK_BYTES + (kk & 3) * 32;
+                    umma_ss(tdP, umma_desc_sw128(dO + off, 16, 1024), umma_desc_sw128(v + off, 16, 1024), idesc_s, kk > 0);
+                }
                 umma_commit(sdp_full);
                 if (last_of_item) umma_commit(&res_empty[rb]);     // the resident pair is only read by these two products
             };
@@ -199,53 +218,57 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
             }
             for (int w = blockIdx.x; w < total && ok; w += gridDim.x, it++) {
                 int fixed, b, h, cnt; decode(w, fixed, b, h, cnt);
-                const int ab = it & 1;
-                const uint32_t acc0 = tAcc + ab * 128, acc1 = acc0 + 64;
+                const int ab = it % ACCBUF;
+                const uint32_t acc0 = tAcc + ab * (2 * HSP), acc1 = acc0 + HSP;
                 for (int n = 0; n < cnt && ok; n++, t++) {
-                    // look one tile ahead (possibly into the next work item)
-                    bool have_next = true, next_new_item = false; int ncnt = cnt, nn = n + 1;
-                    if (nn == cnt) {
-                        if (w + (int)gridDim.x < total) { int f2, b2, h2; decode(w + gridDim.x, f2, b2, h2, ncnt); nn = 0; next_new_item = true; }
-                        else have_next = false;
-                    }
-                    if (have_next) {
+                    // S / dP of the next tile (possibly of the next work item) as soon as the softmax threads hold tile t in registers
+                    auto lookahead = [&]() {
+                        bool have_next = true, next_new_item = false; int ncnt = cnt, nn = n + 1;
+                        if (nn == cnt) {
+                            if (w + (int)gridDim.x < total) { int f2, b2, h2; decode(w + gridDim.x, f2, b2, h2, ncnt); nn = 0; next_new_item = true; }
+                            else have_next = false;
+                        }
+                        if (!have_next) return;
                         const int nit = it + (next_new_item ? 1 : 0);
-                        if (next_new_item) ok = ok && mbar_wait(&res_full[nit & 1], (nit >> 1) & 1, abort_flag, a.status, 0x615);
+                        if (next_new_item) ok = ok && mbar_wait(&res_full[nit % RB], (nit / RB) & 1, abort_flag, a.status, 0x615);
                         int nst = cst + 1; uint32_t nph = cph;
                         if (nst == XSTAGES) { nst = 0; nph ^= 1; }
                         ok = ok && mbar_wait(&x_full[nst], nph, abort_flag, a.status, 0x612);
                         ok = ok && mbar_wait(sdp_empty, t & 1, abort_flag, a.status, 0x613);
-                        if (!ok) break;
+                        if (!ok) return;
                         tc_fence_after();
-                        issue_sdp(nst, nit & 1, nn == ncnt - 1);
-                    }
-                    if (n == 0) ok = ok && mbar_wait(&acc_empty[ab], ((it >> 1) & 1) ^ 1, abort_flag, a.status, 0x616);
+                        issue_sdp(nst, nit % RB, nn == ncnt - 1);
+                    };
+                    if (XSTAGES > 1) { lookahead(); if (!ok) break; }
+                    if (n == 0) ok = ok && mbar_wait(&acc_empty[ab], ((it / ACCBUF) & 1) ^ 1, abort_flag, a.status, 0x616);
                     ok = ok && mbar_wait(pds_full, t & 1, abort_flag, a.status, 0x614);
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t xs = smem_u32(sStr + cst * PAIR_BYTES);
                     const uint32_t p = smem_u32(sP), ds = smem_u32(sdS);
-                    if (a.dbg & 2) {
-                    } else if (DKV) {
-                        // dV += P^T dO ; dK += dS^T Q : A is MN-major (two 64-wide groups 16 KB apart), K = 128 query rows
+                    if (DKV) {
+                        // dV += P^T dO ; dK += dS^T Q : A is MN-major (two 64-wide groups 16 KB apart), K = 128 query rows;
+                        // B = dO / Q tile as an N-major operand (NC groups of 64 channels, 16 KB apart)
                         #pragma unroll
                         for (int kk = 0; kk < BT / 16; kk++)
-                            umma_ss(acc0, umma_desc_sw128(p + kk * 2048, BT * 128, 1024), umma_desc_sw128(xs + TILE_BYTES + kk * 2048, 8192, 1024),
+                            umma_ss(acc0, umma_desc_sw128(p + kk * 2048, BT * 128, 1024), umma_desc_sw128(xs + TILE_BYTES + kk * 2048, CHUNK_BYTES, 1024),
                                     idesc_acc, (n > 0 || kk > 0));
                         #pragma unroll
                         for (int kk = 0; kk < BT / 16; kk++)
-                            umma_ss(acc1, umma_desc_sw128(ds + kk * 2048, BT * 128, 1024), umma_desc_sw128(xs + kk * 2048, 8192, 1024),
+                            umma_ss(acc1, umma_desc_sw128(ds + kk * 2048, BT * 128, 1024), umma_desc_sw128(xs + kk * 2048, CHUNK_BYTES, 1024),
                                     idesc_acc, (n > 0 || kk > 0));
                     } else {
                         // dQ += dS K : A K-major (two 64-column chunks), B = K_j as an N-major operand
                         #pragma unroll
                         for (int kk = 0; kk < BT / 16; kk++)
                             umma_ss(acc0, umma_desc_sw128(ds + (kk >> 2) * (BT * 128) + (kk & 3) * 32, 16, 1024),
-                                    umma_desc_sw128(xs + kk * 2048, 8192, 1024), idesc_acc, (n > 0 || kk > 0));
+                                    umma_desc_sw128(xs + kk * 2048, CHUNK_BYTES, 1024), idesc_acc, (n > 0 || kk > 0));
                     }
                     umma_commit(&x_empty[cst]);
                     umma_commit(pds_empty);
                     if (n == cnt - 1) umma_commit(&acc_full[ab]);
+                    // with a single stream stage the next tile can only be loaded once these MMAs have released it
+                    if (XSTAGES == 1) { lookahead(); if (!ok) break; }
                     if (++cst == XSTAGES) { cst = 0; cph ^= 1; }
                 }
             }
@@ -306,16 +329,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
                         pp[e >> 1] = pack_bf16x2(p0, p1);
                         dd[e >> 1] = pack_bf16x2(d0, d1);
                     }
-                } else if (a.dbg & 1) {
-                    #pragma unroll
-                    for (int e = 0; e < 32; e += 2) {
-                        const float p0 = fmaf(__uint_as_float(sv[e]), a.scale_log2e, -lse_l2);
-                        const float p1 = fmaf(__uint_as_float(sv[e + 1]), a.scale_log2e, -lse_l2);
-                        const float d0 = p0 * fmaf(__uint_as_float(dv[e]), a.scale, -dlt_s);
-                        const float d1 = p1 * fmaf(__uint_as_float(dv[e + 1]), a.scale, -dlt_s);
-                        pp[e >> 1] = pack_bf16x2(p0, p1);
-                        dd[e >> 1] = pack_bf16x2(d0, d1);
-                    }
                 } else {
                     #pragma unroll
                     for (int e = 0; e < 32; e += 2) {
@@ -331,7 +344,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
                 // 64-column chunk (cq >> 1), 16-byte units (cq & 1) * 4 .. +3 of this row, 128-byte swizzle
                 uint8_t* prow = sP + (cq >> 1) * (BT * 128) + r * 128;
                 uint8_t* drow = sdS + (cq >> 1) * (BT * 128) + r * 128;
-                if (!(a.dbg & 4))
                 #pragma unroll
                 for (int u = 0; u < 4; u++) {
                     const int pos = ((((cq & 1) * 4) + u) ^ (r & 7)) * 16;
@@ -344,12 +356,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
                 if (fetch_next) { lse_l2 = nxt_lse * log2e; dlt_s = nxt_dlt * a.scale; row_ok = nxt_ok; }
             }
             // ---- item epilogue: accumulators -> global; the MMA warp is already working on the next item
-            const int ab = it & 1;
-            ok = mbar_wait(&acc_full[ab], (it >> 1) & 1, abort_flag, a.status, 0x622) && ok;
+            const int ab = it % ACCBUF;
+            ok = mbar_wait(&acc_full[ab], (it / ACCBUF) & 1, abort_flag, a.status, 0x622) && ok;
             tc_fence_after();
-            uint32_t v0[16], v1[16];
-            tmem_ld16(tAcc + ab * 128 + lane_off + cq * 16, v0);
-            if (DKV) tmem_ld16(tAcc + ab * 128 + 64 + lane_off + cq * 16, v1);
+            uint32_t v0[16 * NC], v1[16 * NC];
+            #pragma unroll
+            for (int c = 0; c < NC; c++) {
+                tmem_ld16(tAcc + ab * (2 * HSP) + c * 64 + lane_off + cq * 16, v0 + c * 16);
+                if (DKV) tmem_ld16(tAcc + ab * (2 * HSP) + HSP + c * 64 + lane_off + cq * 16, v1 + c * 16);
+            }
             tmem_ld_wait();
             tc_fence_before();
             __syncwarp();
@@ -357,26 +372,26 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
             const int trow = fixed * BT + r;
             if (trow < a.T && ok) {
                 // DKV: acc0 = dV (slot 2), acc1 = dK (slot 1); else acc0 = dQ (slot 0)
-                bf16* dst0 = a.dqkv + (((size_t)b * a.T + trow) * 3 + (DKV ? 2 : 0)) * a.NH * HS + (size_t)h * HS + cq * 16;
+                bf16* dst0 = a.dqkv + (((size_t)b * a.T + trow) * 3 + (DKV ? 2 : 0)) * a.NH * a.hs + (size_t)h * a.hs;
+                bf16* dst1 = a.dqkv + (((size_t)b * a.T + trow) * 3 + 1) * a.NH * a.hs + (size_t)h * a.hs;
                 #pragma unroll
-                for (int e = 0; e < 16; e += 8) {
-                    uint4 o;
-                    o.x = pack_bf16x2(__uint_as_float(v0[e]), __uint_as_float(v0[e + 1]));
-                    o.y = pack_bf16x2(__uint_as_float(v0[e + 2]), __uint_as_float(v0[e + 3]));
-                    o.z = pack_bf16x2(__uint_as_float(v0[e + 4]), __uint_as_float(v0[e + 5]));
-                    o.w = pack_bf16x2(__uint_as_float(v0[e + 6]), __uint_as_float(v0[e + 7]));
-                    *reinterpret_cast<uint4*>(dst0 + e) = o;
-                }
-                if (DKV) {
-                    bf16* dst1 = a.dqkv + (((size_t)b * a.T + trow) * 3 + 1) * a.NH * HS + (size_t)h * HS + cq * 16;
+                for (int c = 0; c < NC; c++) {
                     #pragma unroll
                     for (int e = 0; e < 16; e += 8) {
-                        uint4 o;
-                        o.x = pack_bf16x2(__uint_as_float(v1[e]), __uint_as_float(v1[e + 1]));
-                        o.y = pack_bf16x2(__uint_as_float(v1[e + 2]), __uint_as_float(v1[e + 3]));
-                        o.z = pack_bf16x2(__uint_as_float(v1[e + 4]), __uint_as_float(v1[e + 5]));
-                        o.w = pack_bf16x2(__uint_as_float(v1[e + 6]), __uint_as_float(v1[e + 7]));
-                        *reinterpret_cast<uint4*>(dst1 + e) = o;
+                        const int col = c * 64 + cq * 16 + e;
+                        if (col < a.hs) {
+                            const uint32_t* x0 = v0 + c * 16 + e;
+                            uint4 o;
+                            o.x = pack_bf16x2(__uint_as_float(x0[0]), __uint_as_float(x0[1])); o.y = pack_bf16x2(__uint_as_float(x0[2]), __uint_as_float(x0[3]));
+                            o.z = pack_bf16x2(__uint_as_float(x0[4]), __uint_as_float(x0[5])); o.w = pack_bf16x2(__uint_as_float(x0[6]), __uint_as_float(x0[7]));
+                            *reinterpret_cast<uint4*>(dst0 + col) = o;
+                            if (DKV) {
+                                const uint32_t* x1 = v1 + c * 16 + e;
+                                o.x = pack_bf16x2(__uint_as_float(x1[0]), __uint_as_float(x1[1])); o.y = pack_bf16x2(__uint_as_float(x1[2]), __uint_as_float(x1[3]));
+                                o.z = pack_bf16x2(__uint_as_float(x1[4]), __uint_as_float(x1[5])); o.w = pack_bf16x2(__uint_as_float(x1[6]), __uint_as_float(x1[7]));
+                                *reinterpret_cast<uint4*>(dst1 + col) = o;
+                            }
+                        }
                     }
                 }
             }
@@ -395,10 +410,25 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
 
 }  // namespace
 
-// dqkv (B,T,3,NH,HS) = gradient of causal attention; delta: scratch of B*NH*T floats
+template <int NC>
+int launch_bwd(const CUtensorMap& tmQKV, const CUtensorMap& tmDO, const BwdArgs& a, int grid, cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_kernel<true, NC>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg<NC>::SMEM));
+        CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_kernel<false, NC>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg<NC>::SMEM));
+        configured = true;
+    }
+    attn_bwd_kernel<true, NC><<<grid, BWD_THREADS, BwdCfg<NC>::SMEM, stream>>>(tmQKV, tmDO, a);
+    CUDA_CHECK(cudaGetLastError());
+    attn_bwd_kernel<false, NC><<<grid, BWD_THREADS, BwdCfg<NC>::SMEM, stream>>>(tmQKV, tmDO, a);
+    CUDA_CHECK(cudaGetLastError());
+    return 0;
+}
+
+// dqkv (B,T,3,NH,HS) = gradient of causal attention; delta: scratch of B*NH*T floats.  Head sizes: multiples of 8, 64..128.
 extern "C" int llmc_attention_bwd(bf16* dqkv, float* delta, const bf16* dout, const bf16* qkv, const bf16* out, const float* lse,
                                   int B, int T, int NH, int hs, cudaStream_t stream) {
-    if (hs != HS) { fprintf(stderr, "[llmc_b200] attention backward: head size %d not supported (64 only)\n", hs); return -1; }
+    if (hs < 64 || hs > 128 || (hs % 8)) { fprintf(stderr, "[llmc_b200] attention backward: head size %d not supported (multiples of 8 from 64 to 128)\n", hs); return -1; }
     CUtensorMap tmQKV, tmDO;
     int rc = llmc_attn_qkv_map(&tmQKV, qkv, B, T, NH, hs);
     if (rc) return rc;
@@ -408,27 +438,16 @@ extern "C" int llmc_attention_bwd(bf16* dqkv, float* delta, const bf16* dout, co
         uint32_t box[4] = {64, 1, 128, 1};
         if ((rc = llmc_get_tensormap(&tmDO, dout, 2, 4, dims, strides, box, 3))) return rc;
     }
-    static bool configured = false;
-    if (!configured) {
-        CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM));
-        CUDA_CHECK(cudaFuncSetAttribute(attn_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM));
-        configured = true;
-    }
     const long long rows = (long long)B * T * NH;
-    delta_kernel<<<(unsigned)CEIL_DIV(rows * 8, 256), 256, 0, stream>>>(delta, out, dout, B, T, NH);
+    delta_kernel<<<(unsigned)CEIL_DIV(rows * 8, 256), 256, 0, stream>>>(delta, out, dout, B, T, NH, hs);
     CUDA_CHECK(cudaGetLastError());
     BwdArgs a;
-    a.dqkv = dqkv; a.lse = lse; a.delta = delta; a.B = B; a.T = T; a.NH = NH;
+    a.dqkv = dqkv; a.lse = lse; a.delta = delta; a.B = B; a.T = T; a.NH = NH; a.hs = hs;
     a.scale = 1.0f / sqrtf((float)hs);
     a.scale_log2e = a.scale * 1.4426950408889634f;
     a.status = llmc_status_ptr();
-    { const char* e = getenv("LLMC_ATTN_DBG"); a.dbg = e ? atoi(e) : 0; }
     const int nt = CEIL_DIV(T, BT);
     int sms = llmc_device_sm_count(); if (sms <= 0) sms = 148;
     const int grid = B * NH * nt < sms ? B * NH * nt : sms;
-    if (!(a.dbg & 16)) attn_bwd_kernel<true><<<grid, BWD_THREADS, BWD_SMEM, stream>>>(tmQKV, tmDO, a);
-    CUDA_CHECK(cudaGetLastError());
-    if (!(a.dbg & 32)) attn_bwd_kernel<false><<<grid, BWD_THREADS, BWD_SMEM, stream>>>(tmQKV, tmDO, a);
-    CUDA_CHECK(cudaGetLastError());
-    return 0;
+    return hs <= 64 ? launch_bwd<1>(tmQKV, tmDO, a, grid, stream) : launch_bwd<2>(tmQKV, tmDO, a, grid, stream);
 }

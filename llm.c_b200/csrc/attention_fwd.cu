@@ -1,4 +1,5 @@
-// Causal flash attention forward for sm_100a on the packed (B, T, 3, NH, HS) QKV layout, HS = 64.
+// Causal flash attention forward for sm_100a on the packed (B, T, 3, NH, HS) QKV layout; head sizes 64..128
+// (multiples of 8; sizes above 64 run as a 128-wide head whose missing channels TMA fills with zeros).
 //
 // Persistent: one CTA per SM walks a heavy-first list of (batch, head, 128-row query tile) work items; Q is double
 // buffered so the next item's loads and first MMA run under the current item's tail.  Roles inside a CTA (576 threads):
@@ -20,20 +21,28 @@
 
 namespace {
 
-constexpr int HS = 64;
 constexpr int BQ = 128, BKV = 128;
-constexpr int TILE_BYTES = 128 * HS * 2;           // 16 KB: a 128 x 64 bf16 tile
+constexpr int CHUNK_BYTES = 128 * 64 * 2;          // 16 KB: 128 rows x 64 channels of bf16, one 128-byte-swizzled TMA box
 constexpr int P_BYTES = BQ * BKV * 2;              // 32 KB
 constexpr int XCH_BYTES = (2 * 4 * 128 + 4 * 128) * 4;     // row-max exchange (double buffered) + final row sums
-constexpr int KVSTAGES = 3;
-constexpr int FWD_SMEM = 2 * TILE_BYTES /*Q*/ + KVSTAGES * TILE_BYTES /*K*/ + KVSTAGES * TILE_BYTES /*V*/ + 2 * P_BYTES + XCH_BYTES + 256;
 constexpr int FWD_THREADS = 576;                   // TMA warp + MMA warp + 16 softmax warps
-constexpr int FWD_TMEM_COLS = 256;
+
+// NC = number of 64-channel chunks of the (zero-padded) head: 1 -> head size 64, 2 -> head sizes 72..128.
+// The wider variant trades buffering for capacity (single Q / P buffers, two K/V stages) to stay within shared memory.
+template <int NC> struct FwdCfg {
+    static constexpr int HSP = 64 * NC;
+    static constexpr int TILE_BYTES = NC * CHUNK_BYTES;
+    static constexpr int QBUF = NC == 1 ? 2 : 1;
+    static constexpr int KVSTAGES = NC == 1 ? 3 : 2;
+    static constexpr int PBUF = NC == 1 ? 2 : 1;
+    static constexpr int SMEM = QBUF * TILE_BYTES + 2 * KVSTAGES * TILE_BYTES + PBUF * P_BYTES + XCH_BYTES + 256;
+    static constexpr int TMEM_COLS = NC == 1 ? 256 : 512;      // S (128) + two O buffers of HSP columns
+};
 
 struct FwdArgs {
     bf16* out;         // (B, T, NH, HS)
     float* lse;        // (B, NH, T)
-    int B, T, NH;
+    int B, T, NH, hs;
     float scale_log2e; // (1/sqrt(HS)) * log2(e)
     float scale;
     unsigned int* status;
@@ -41,14 +50,17 @@ struct FwdArgs {
 
 DEVINL void quarter_barrier(int q) { asm volatile("bar.sync %0, 128;" ::"r"(1 + q) : "memory"); }
 
+template <int NC>
 __global__ void __launch_bounds__(FWD_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FwdArgs a) {
+    using Cfg = FwdCfg<NC>;
+    constexpr int HSP = Cfg::HSP, TILE_BYTES = Cfg::TILE_BYTES, QBUF = Cfg::QBUF, KVSTAGES = Cfg::KVSTAGES, PBUF = Cfg::PBUF;
     extern __shared__ __align__(1024) uint8_t smem[];
-    uint8_t* sQ = smem;                        // 2 buffers (current / next work item)
-    uint8_t* sK = sQ + 2 * TILE_BYTES;         // KVSTAGES stages
+    uint8_t* sQ = smem;                        // QBUF buffers (current / next work item)
+    uint8_t* sK = sQ + QBUF * TILE_BYTES;      // KVSTAGES stages
     uint8_t* sV = sK + KVSTAGES * TILE_BYTES;  // KVSTAGES stages
-    uint8_t* sP = sV + KVSTAGES * TILE_BYTES;  // 2 buffers
-    float* xmax = reinterpret_cast<float*>(sP + 2 * P_BYTES);      // [2][4][128]
+    uint8_t* sP = sV + KVSTAGES * TILE_BYTES;  // PBUF buffers
+    float* xmax = reinterpret_cast<float*>(sP + PBUF * P_BYTES);   // [2][4][128]
     float* xsum = xmax + 2 * 4 * 128;                              // [4][128]
     uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(xmax) + XCH_BYTES);
     uint64_t* q_full = bars + 0;     // [2]
@@ -84,12 +96,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FwdArgs a) {
         mbar_fence_init();
         tma_prefetch_desc(&tmQKV);
     }
-    if (warp == 1) { tmem_alloc(tmem_slot, FWD_TMEM_COLS); tmem_relinquish(); }
+    if (warp == 1) { tmem_alloc(tmem_slot, Cfg::TMEM_COLS); tmem_relinquish(); }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tS = tmem_base, tO = tmem_base + 128;       // O partial products: two 64-column buffers
+    const uint32_t tS = tmem_base, tO = tmem_base + 128;       // O partial products: two buffers of HSP columns
 
     if (warp == 0) {
         if (lane == 0) {
@@ -97,10 +109,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FwdArgs a) {
             int it = 0;
             for (int w = blockIdx.x; w < total; w += gridDim.x, it++) {
                 int qi, b, h; decode(w, qi, b, h);
-                const int qb = it & 1;
-                if (!mbar_wait(&q_empty[qb], ((it >> 1) & 1) ^ 1, abort_flag, a.status, 0x502)) break;
+                const int qb = it % QBUF;
+                if (!mbar_wait(&q_empty[qb], ((it / QBUF) & 1) ^ 1, abort_flag, a.status, 0x502)) break;
                 mbar_expect_tx(&q_full[qb], TILE_BYTES);
-                tma_load_4d(sQ + qb * TILE_BYTES, &tmQKV, &q_full[qb], 0, h, qi * BQ, b);
+                #pragma unroll
+                for (int c = 0; c < NC; c++) tma_load_4d(sQ + qb * TILE_BYTES + c * CHUNK_BYTES, &tmQKV, &q_full[qb], c * 64, h, qi * BQ, b);
                 bool fail = false;
                 for (int j = 0; j <= qi; j++) {
                     const int st = kst;
@@ -108,10 +121,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FwdArgs a) {
                     if (++kst == KVSTAGES) { kst = 0; kph ^= 1; }
                     if (!mbar_wait(&k_empty[st], ph, abort_flag, a.status, 0x500)) { fail = true; break; }
                     mbar_expect_tx(&k_full[st], TILE_BYTES);
-                    tma_load_4d(sK + st * TILE_BYTES, &tmQKV, &k_full[st], 0, a.NH + h, j * BKV, b);
+                    #pragma unroll
+                    for (int c = 0; c < NC; c++) tma_load_4d(sK + st * TILE_BYTES + c * CHUNK_BYTES, &tmQKV, &k_full[st], c * 64, a.NH + h, j * BKV, b);
                     if (!mbar_wait(&v_empty[st], ph, abort_flag, a.status, 0x501)) { fail = true; break; }
                     mbar_expect_tx(&v_full[st], TILE_BYTES);
-                    tma_load_4d(sV + st * TILE_BYTES, &tmQKV, &v_full[st], 0, 2 * a.NH + h, j * BKV, b);
+                    #pragma unroll
+                    for (int c = 0; c < NC; c++) tma_load_4d(sV + st * TILE_BYTES + c * CHUNK_BYTES, &tmQKV, &v_full[st], c * 64, 2 * a.NH + h, j * BKV, b);
                 }
                 if (fail) break;
             }
@@ -119,12 +134,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FwdArgs a) {
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc_s = umma_idesc_bf16(BQ, BKV, 0, 0);     // Q (K-major) x K (K-major)
-            constexpr uint32_t idesc_o = umma_idesc_bf16(BQ, HS, 0, 1);      // P (K-major) x V (N-major)
+            constexpr uint32_t idesc_o = umma_idesc_bf16(BQ, HSP, 0, 1);     // P (K-major) x V (N-major)
             auto issue_s = [&](int st, int qb, bool last_of_item) {
                 const uint32_t q = smem_u32(sQ + qb * TILE_BYTES), k = smem_u32(sK + st * TILE_BYTES);
                 #pragma unroll
-                for (int kk = 0; kk < HS / 16; kk++)
-                    umma_ss(tS, umma_desc_sw128(q + kk * 32, 16, 1024), umma_desc_sw128(k + kk * 32, 16, 1024), idesc_s, kk > 0);
+                for (int kk = 0; kk < HSP / 16; kk++) {      // 64-channel chunks are 16 KB apart, 16 channels = 32 bytes inside a chunk
+                    const uint32_t off = (kk >> 2) * CHUNK_BYTES + (kk & 3) * 32;
+                    umma_ss(tS, umma_desc_sw128(q + off, 16, 1024), umma_desc_sw128(k + off, 16, 1024), idesc_s, kk > 0);
+                }
                 umma_commit(s_full);
                 umma_commit(&k_empty[st]);
                 if (last_of_item) umma_commit(&q_empty[qb]);
@@ -150,25 +167,25 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FwdArgs a) {
                     }
                     if (have_next) {
                         const int nit = it + (new_item ? 1 : 0);
-                        if (new_item) ok = ok && mbar_wait(&q_full[nit & 1], (nit >> 1) & 1, abort_flag, a.status, 0x516);
+                        if (new_item) ok = ok && mbar_wait(&q_full[nit % QBUF], (nit / QBUF) & 1, abort_flag, a.status, 0x516);
                         int nst = cst + 1; uint32_t nph = cph;
                         if (nst == KVSTAGES) { nst = 0; nph ^= 1; }
                         ok = ok && mbar_wait(&k_full[nst], nph, abort_flag, a.status, 0x512);
                         ok = ok && mbar_wait(s_empty, t & 1, abort_flag, a.status, 0x513);
                         if (!ok) break;
                         tc_fence_after();
-                        issue_s(nst, nit & 1, nj == nqi);
+                        issue_s(nst, nit % QBUF, nj == nqi);
                     }
                     ok = ok && mbar_wait(p_full, t & 1, abort_flag, a.status, 0x514);
                     ok = ok && mbar_wait(&v_full[cst], cph, abort_flag, a.status, 0x515);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t p = smem_u32(sP + (t & 1) * P_BYTES), v = smem_u32(sV + cst * TILE_BYTES);
+                    const uint32_t p = smem_u32(sP + (t % PBUF) * P_BYTES), v = smem_u32(sV + cst * TILE_BYTES);
                     #pragma unroll
                     for (int kk = 0; kk < BKV / 16; kk++) {
                         // P: two 64-column swizzled chunks of 16 KB; V: 128 kv rows of 128 B, 16 rows per K step
                         const uint32_t pa = p + (kk >> 2) * (BQ * 128) + (kk & 3) * 32;
-                        umma_ss(tO + (t & 1) * 64, umma_desc_sw128(pa, 16, 1024), umma_desc_sw128(v + kk * 2048, 8192, 1024), idesc_o, kk > 0);
+                        umma_ss(tO + (t & 1) * HSP, umma_desc_sw128(pa, 16, 1024), umma_desc_sw128(v + kk * 2048, CHUNK_BYTES, 1024), idesc_o, kk > 0);
                     }
                     umma_commit(&o_full[t & 1]);
                     umma_commit(&v_empty[cst]);
@@ -188,9 +205,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FwdArgs a) {
         for (int w = blockIdx.x; w < total; w += gridDim.x) {
             int qi, b, h; decode(w, qi, b, h);
             float m = -INFINITY, l = 0.f;
-            float O[16];
+            float O[16 * NC];                  // columns c*64 + cq*16 .. +15 of every 64-channel chunk c
             #pragma unroll
-            for (int d = 0; d < 16; d++) O[d] = 0.f;
+            for (int d = 0; d < 16 * NC; d++) O[d] = 0.f;
+            // adds the finished P V of tile `tt` to the running output (optionally rescaled afterwards)
+            auto fold = [&](uint32_t tt, float rescale) {
+                ok = mbar_wait(&o_full[tt & 1], (tt >> 1) & 1, abort_flag, a.status, 0x521) && ok;
+                tc_fence_after();
+                #pragma unroll
+                for (int c = 0; c < NC; c++) {
+                    uint32_t ov[16];
+                    tmem_ld16(tO + (tt & 1) * HSP + c * 64 + lane_off + cq * 16, ov);
+                    tmem_ld_wait();
+                    #pragma unroll
+                    for (int d = 0; d < 16; d++) O[c * 16 + d] = (O[c * 16 + d] + __uint_as_float(ov[d])) * rescale;
+                }
+                tc_fence_before();
+            };
             for (int j = 0; j <= qi; j++, t++) {
                 ok = mbar_wait(s_full, t & 1, abort_flag, a.status, 0x520) && ok;
                 tc_fence_after();
@@ -230,7 +261,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FwdArgs a) {
                     pk[e >> 1] = pack_bf16x2(p0, p1);
                 }
                 l = l * alpha + rs;
-                uint8_t* prow = sP + (t & 1) * P_BYTES + (cq >> 1) * (BQ * 128) + r * 128;
+                if (PBUF == 1 && j > 0) fold(t - 1, alpha);      // single P buffer: the previous P V must have consumed it
+                uint8_t* prow = sP + (t % PBUF) * P_BYTES + (cq >> 1) * (BQ * 128) + r * 128;
                 #pragma unroll
                 for (int u = 0; u < 4; u++) {
                     const int pos = ((((cq & 1) * 4) + u) ^ (r & 7)) * 16;
@@ -240,28 +272,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FwdArgs a) {
                 __syncwarp();
                 if (lane == 0) mbar_arrive(p_full);
                 // fold in the previous tile's P V (rescaled to the new maximum together with the running output)
-                if (j > 0) {
-                    ok = mbar_wait(&o_full[(t - 1) & 1], ((t - 1) >> 1) & 1, abort_flag, a.status, 0x521) && ok;
-                    tc_fence_after();
-                    uint32_t ov[16];
-                    tmem_ld16(tO + ((t - 1) & 1) * 64 + lane_off + cq * 16, ov);
-                    tmem_ld_wait();
-                    tc_fence_before();
-                    #pragma unroll
-                    for (int d = 0; d < 16; d++) O[d] = (O[d] + __uint_as_float(ov[d])) * alpha;
-                }
+                if (PBUF != 1 && j > 0) fold(t - 1, alpha);
             }
-            // last tile of the item
-            ok = mbar_wait(&o_full[(t - 1) & 1], ((t - 1) >> 1) & 1, abort_flag, a.status, 0x522) && ok;
-            tc_fence_after();
-            {
-                uint32_t ov[16];
-                tmem_ld16(tO + ((t - 1) & 1) * 64 + lane_off + cq * 16, ov);
-                tmem_ld_wait();
-                tc_fence_before();
-                #pragma unroll
-                for (int d = 0; d < 16; d++) O[d] += __uint_as_float(ov[d]);
-            }
+            fold(t - 1, 1.0f);      // last tile of the item
             // total row sum over the four quarters
             xsum[cq * 128 + r] = l;
             quarter_barrier(q);
@@ -269,13 +282,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FwdArgs a) {
             const int trow = qi * BQ + r;
             if (trow < a.T && ok) {
                 const float inv = 1.0f / l;
-                bf16* op = a.out + (((size_t)b * a.T + trow) * a.NH + h) * HS + cq * 16;
+                bf16* op = a.out + (((size_t)b * a.T + trow) * a.NH + h) * a.hs;
                 #pragma unroll
-                for (int d = 0; d < 16; d += 8) {
-                    uint4 o;
-                    o.x = pack_bf16x2(O[d] * inv, O[d + 1] * inv); o.y = pack_bf16x2(O[d + 2] * inv, O[d + 3] * inv);
-                    o.z = pack_bf16x2(O[d + 4] * inv, O[d + 5] * inv); o.w = pack_bf16x2(O[d + 6] * inv, O[d + 7] * inv);
-                    *reinterpret_cast<uint4*>(op + d) = o;
+                for (int c = 0; c < NC; c++) {
+                    #pragma unroll
+                    for (int d = 0; d < 16; d += 8) {
+                        const int col = c * 64 + cq * 16 + d;
+                        if (col < a.hs) {          // head sizes are multiples of 8: whole 16-byte groups
+                            const float* Oc = O + c * 16 + d;
+                            uint4 o;
+                            o.x = pack_bf16x2(Oc[0] * inv, Oc[1] * inv); o.y = pack_bf16x2(Oc[2] * inv, Oc[3] * inv);
+                            o.z = pack_bf16x2(Oc[4] * inv, Oc[5] * inv); o.w = pack_bf16x2(Oc[6] * inv, Oc[7] * inv);
+                            *reinterpret_cast<uint4*>(op + col) = o;
+                        }
+                    }
                 }
                 if (cq == 0) a.lse[((size_t)b * a.NH + h) * a.T + trow] = m * a.scale + logf(l);
             }
@@ -289,7 +309,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FwdArgs a) {
         while (clock64() - t0 < 2000000ll) { __nanosleep(1000); }
         __syncthreads();
     }
-    if (warp == 1) tmem_dealloc(tmem_base, FWD_TMEM_COLS);
+    if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
 }
 
 }  // namespace
@@ -302,26 +322,31 @@ int llmc_attn_qkv_map(CUtensorMap* tm, const bf16* qkv, int B, int T, int NH, in
     return llmc_get_tensormap(tm, qkv, 2, 4, dims, strides, box, 3);
 }
 
-// out (B,T,NH,HS) = causal softmax(Q K^T / sqrt(HS)) V ; lse (B,NH,T) fp32
+template <int NC>
+int launch_fwd(const CUtensorMap& tm, const FwdArgs& a, int grid, cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        CUDA_CHECK(cudaFuncSetAttribute(attn_fwd_kernel<NC>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdCfg<NC>::SMEM));
+        configured = true;
+    }
+    attn_fwd_kernel<NC><<<grid, FWD_THREADS, FwdCfg<NC>::SMEM, stream>>>(tm, a);
+    CUDA_CHECK(cudaGetLastError());
+    return 0;
+}
+
+// out (B,T,NH,HS) = causal softmax(Q K^T / sqrt(HS)) V ; lse (B,NH,T) fp32.  Head sizes: multiples of 8 up to 128.
 extern "C" int llmc_attention_fwd(bf16* out, float* lse, const bf16* qkv, int B, int T, int NH, int hs, cudaStream_t stream) {
-    if (hs != HS) { fprintf(stderr, "[llmc_b200] attention: head size %d not supported (64 only)\n", hs); return -1; }
+    if (hs < 64 || hs > 128 || (hs % 8)) { fprintf(stderr, "[llmc_b200] attention: head size %d not supported (multiples of 8 from 64 to 128)\n", hs); return -1; }
     CUtensorMap tm;
     int rc = llmc_attn_qkv_map(&tm, qkv, B, T, NH, hs);
     if (rc) return rc;
-    static bool configured = false;
-    if (!configured) {
-        CUDA_CHECK(cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM));
-        configured = true;
-    }
     FwdArgs a;
-    a.out = out; a.lse = lse; a.B = B; a.T = T; a.NH = NH;
+    a.out = out; a.lse = lse; a.B = B; a.T = T; a.NH = NH; a.hs = hs;
     a.scale = 1.0f / sqrtf((float)hs);
     a.scale_log2e = a.scale * 1.4426950408889634f;
     a.status = llmc_status_ptr();
     const int nq = CEIL_DIV(T, BQ);
     int sms = llmc_device_sm_count(); if (sms <= 0) sms = 148;
     const int grid = B * NH * nq < sms ? B * NH * nq : sms;
-    attn_fwd_kernel<<<grid, FWD_THREADS, FWD_SMEM, stream>>>(tm, a);
-    CUDA_CHECK(cudaGetLastError());
-    return 0;
+    return hs <= 64 ? launch_fwd<1>(tm, a, grid, stream) : launch_fwd<2>(tm, a, grid, stream);
 }

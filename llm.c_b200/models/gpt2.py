@@ -54,11 +54,15 @@ def gpt2_descriptor(depth):
 
 def gpt3_descriptor(channels):
     """GPT-3 family by width (reference train_gpt2.cu:538-560); context 2048."""
-    table = {384: (6, 6), 768: (12, 12), 1024: (24, 16), 1536: (24, 16), 2048: (24, 16), 2560: (32, 32), 4096: (32, 32),
-             5140: (40, 40), 12288: (96, 96)}
+    # width -> (depth, head size); the number of heads follows
+    table = {384: (6, 64), 768: (12, 64), 1024: (24, 64), 1536: (24, 96), 2048: (24, 128), 2560: (32, 80), 4096: (32, 128),
+             5140: (40, 128), 12288: (96, 128)}
     if channels not in table:
         raise ValueError("unsupported GPT-3 width %d" % channels)
-    L, nh = table[channels]
+    L, hs = table[channels]
+    if channels % hs:
+        raise ValueError("GPT-3 width %d is not divisible by its head size %d" % (channels, hs))
+    nh = channels // hs
     return GPTConfig(2048, 50257, 50304, L, nh, channels)
 
 
@@ -98,8 +102,8 @@ class GPT:
             dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
         if self.device.type == "cuda" and dtype != torch.bfloat16:
             raise ValueError("the sm_100a kernels are bf16; use the CPU path for fp32")
-        if cfg.channels % 8 or (self.device.type == "cuda" and cfg.head_size != 64):
-            raise ValueError("channels must be a multiple of 8 and (on the GPU) the head size 64")
+        if cfg.channels % 8 or (self.device.type == "cuda" and (cfg.head_size % 8 or not 64 <= cfg.head_size <= 128)):
+            raise ValueError("channels must be a multiple of 8 and (on the GPU) the head size a multiple of 8 from 64 to 128")
         self.dtype = dtype
         self.recompute = recompute
         self.shapes = param_shapes(cfg)

@@ -251,9 +251,9 @@ def test_global_norm_and_adamw():
     assert torch.equal(p2, params)
 
 
-@pytest.mark.parametrize("B,T,NH", [(2, 128, 2), (1, 64, 3), (2, 384, 4), (1, 1024, 2)])
-def test_attention_forward(B, T, NH):
-    hs = 64
+@pytest.mark.parametrize("B,T,NH,hs", [(2, 128, 2, 64), (1, 64, 3, 64), (2, 384, 4, 64), (1, 1024, 2, 64), (2, 384, 2, 128), (1, 200, 3, 96),
+                                        (2, 256, 2, 80)])
+def test_attention_forward(B, T, NH, hs):
     qkv = rnd(B, T, 3 * NH * hs)
     out = torch.full((B, T, NH * hs), float("nan"), dtype=torch.bfloat16, device=DEV)
     lse = torch.empty(B, NH, T, device=DEV)
@@ -264,9 +264,9 @@ def test_attention_forward(B, T, NH):
     close(out, ro, 2e-2, 2e-2, "attention out")
 
 
-@pytest.mark.parametrize("B,T,NH", [(1, 128, 1), (2, 64, 2), (2, 384, 3), (1, 1024, 2)])
-def test_attention_backward(B, T, NH):
-    hs = 64
+@pytest.mark.parametrize("B,T,NH,hs", [(1, 128, 1, 64), (2, 64, 2, 64), (2, 384, 3, 64), (1, 1024, 2, 64), (2, 384, 2, 128), (1, 200, 3, 96),
+                                        (2, 256, 2, 80)])
+def test_attention_backward(B, T, NH, hs):
     qkv = rnd(B, T, 3 * NH * hs)
     dout = rnd(B, T, NH * hs, scale=0.5, seed=9)
     dev_qkv = qkv.to(DEV)

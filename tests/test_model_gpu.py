@@ -68,3 +68,21 @@ def test_gpu_training_reduces_loss_and_is_deterministic():
     l1, p1 = runs[1]
     assert l0[0] > math.log(1000) - 0.5 and l0[-1] < l0[0] - 0.5, l0
     assert l0 == l1 and torch.equal(p0, p1), "two identical runs must agree bit for bit"
+
+
+@pytest.mark.parametrize("C,NH", [(256, 2), (192, 2), (160, 2)])
+def test_gpu_matches_cpu_reference_wide_heads(C, NH):
+    """Head sizes 128, 96 and 80 (the GPT-3 family) run on the 128-wide attention kernels."""
+    gm = make("cuda", torch.bfloat16, 0, L=2, C=C, NH=NH, T=256)
+    cm = make("cpu", torch.float32, 0, L=2, C=C, NH=NH, T=256)
+    cm.params_flat.copy_(gm.params_flat.float().cpu())
+    x, y = batch(gm.cfg, 2, 200)
+    cm.forward(x, y)
+    cm.backward()
+    gm.forward(x.cuda(), y.cuda())
+    gm.backward()
+    assert abs(float(gm.loss()) - float(cm.loss())) < 2e-2
+    for name in gpt2.PARAM_NAMES:
+        got, want = gm.grads[name].float().cpu(), cm.grads[name]
+        scale = want.abs().max().item() + 1e-6
+        assert (got - want).abs().max().item() < 0.06 * scale + 1e-4, name
