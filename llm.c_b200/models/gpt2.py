@@ -21,6 +21,21 @@ import torch
 
 from .. import ops
 
+
+class _Range:
+    """NVTX range on CUDA devices (the reference's NvtxRange, llmc/cuda_common.h:115-124); a no-op elsewhere."""
+
+    def __init__(self, name, on):
+        self.name, self.on = name, on
+
+    def __enter__(self):
+        if self.on:
+            torch.cuda.nvtx.range_push(self.name)
+
+    def __exit__(self, *exc):
+        if self.on:
+            torch.cuda.nvtx.range_pop()
+
 PARAM_NAMES = ["wte", "wpe", "ln1w", "ln1b", "qkvw", "qkvb", "attprojw", "attprojb", "ln2w", "ln2b", "fcw", "fcb",
                "fcprojw", "fcprojb", "lnfw", "lnfb"]
 # tensors that receive weight decay (2-D weights): reference train_gpt2.cu:1080
@@ -213,9 +228,11 @@ class GPT:
         L, C, NH = cfg.num_layers, cfg.channels, cfg.num_heads
         if tokens.data_ptr() != self.inputs.data_ptr():
             self.inputs.copy_(tokens, non_blocking=True)
+        nvtx = self.device.type == "cuda"
         ops.encoder_forward(a["encoded"], self.inputs, p["wte"], p["wpe"])
         ops.layernorm_forward(a["ln1"][0], a["ln1_mean"][0], a["ln1_rstd"][0], a["encoded"], p["ln1w"][0], p["ln1b"][0])
         for l in range(L):
+          with _Range("forward layer %d" % l, nvtx):
             lln = 0 if self.recompute >= 2 else l
             lg = 0 if self.recompute >= 1 else l
             residual = a["encoded"] if l == 0 else a["residual3"][l - 1]
@@ -269,7 +286,9 @@ class GPT:
         ops.matmul_wgrad(g["wte"], dlogits, a["lnf"], accumulate=acc)
         ops.layernorm_backward(dres, g["lnfw"], g["lnfb"], dl_btc, a["residual3"][L - 1], p["lnfw"], a["lnf_mean"], a["lnf_rstd"],
                                accumulate_dinp=False, accumulate_dwdb=acc)
+        nvtx = self.device.type == "cuda"
         for l in reversed(range(L)):
+          with _Range("backward layer %d" % l, nvtx):
             residual = a["encoded"] if l == 0 else a["residual3"][l - 1]
             lln = 0 if self.recompute >= 2 else l
             lg = 0 if self.recompute >= 1 else l
