@@ -45,6 +45,9 @@ def cuda():
         "llmc_tensormap_cache_clear": (None, []),
         "llmc_device_sm_count": (I, []),
         "llmc_gemm": (I, [P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, P, I, S]),
+        "llmc_gemm2": (I, [P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, P, S]),
+        "llmc_gemm2_workspace": (None, [I, I, I, POINTER(c_longlong), POINTER(c_int)]),
+        "llmc_gemm2_pick_splits": (I, [I, I, I, I]),
         "llmc_gemm_workspace": (None, [I, I, I, POINTER(c_longlong), POINTER(c_int)]),
         "llmc_gemm_pick_splits": (I, [I, I, I, I]),
         "llmc_layernorm_fwd": (I, [P, P, P, P, P, P, I, I, S]),

@@ -1,5 +1,6 @@
 """Thin launchers of the sm_100a kernels: tensors in, C entry points out (see csrc/*.cu)."""
 import ctypes
+import os
 
 import torch
 
@@ -9,6 +10,8 @@ from .._lib import TensorTable, check
 MODE_STORE, MODE_GELU, MODE_DGELU, MODE_ACCUM = 0, 1, 2, 3
 
 _launches = 0   # number of kernel-library launches issued (bench.py reports it)
+# forward / dgrad GEMMs with at least this many 256 x 256 tiles run on the two-SM kernel (gemm2.cu); 0 disables it
+TWO_SM_MIN_TILES = int(os.environ.get("LLMC_GEMM_2SM_MIN_TILES", "74"))
 
 
 def launch_count():
@@ -50,16 +53,32 @@ def sm_count(device):
 
 
 def gemm(a, b, d, M, N, K, lda, ldb, ldd, a_mn, b_mn, mode, bias=None, aux=None, accumulate=False, splits=1, max_ctas=0):
+    """Dispatches to the two-SM kernel (256 x 256 tiles on CTA pairs) for problems with enough tiles, else to the single-CTA one."""
     global _launches
     lib = _lib.cuda()
+    _launches += 1
+    tiles256 = ((M + 255) // 256) * ((N + 255) // 256)
+    if mode == MODE_ACCUM:
+        two_sm = TWO_SM_MIN_TILES > 0 and a_mn and b_mn and tiles256 >= 8
+    else:
+        two_sm = TWO_SM_MIN_TILES > 0 and not a_mn and tiles256 >= TWO_SM_MIN_TILES
     ws = cnt = None
+    if two_sm:
+        if mode == MODE_ACCUM:
+            splits = lib.llmc_gemm2_pick_splits(M, N, K, sm_count(d.device))
+            wsf, nc = ctypes.c_longlong(0), ctypes.c_int(0)
+            lib.llmc_gemm2_workspace(M, N, splits, ctypes.byref(wsf), ctypes.byref(nc))
+            if splits > 1:
+                ws = _scratch.get("gemm_ws", wsf.value, torch.float32, d.device)
+            cnt = _scratch.get("gemm2_cnt", nc.value, torch.int32, d.device, zero=True)
+        check(lib.llmc_gemm2(_p(a), _p(b), _p(d), _p(bias), _p(aux), M, N, K, lda, ldb, ldd, int(a_mn), int(b_mn), mode, int(accumulate), splits,
+                             _p(ws), _p(cnt), _stream()), "llmc_gemm2")
+        return
     if mode == MODE_ACCUM and splits > 1:
-        wsf = ctypes.c_longlong(0)
-        nc = ctypes.c_int(0)
+        wsf, nc = ctypes.c_longlong(0), ctypes.c_int(0)
         lib.llmc_gemm_workspace(M, N, splits, ctypes.byref(wsf), ctypes.byref(nc))
         ws = _scratch.get("gemm_ws", wsf.value, torch.float32, d.device)
         cnt = _scratch.get("gemm_cnt", nc.value, torch.int32, d.device, zero=True)
-    _launches += 1
     check(lib.llmc_gemm(_p(a), _p(b), _p(d), _p(bias), _p(aux), M, N, K, lda, ldb, ldd, int(a_mn), int(b_mn), mode,
                         int(accumulate), splits, _p(ws), _p(cnt), max_ctas, _stream()), "llmc_gemm")
 

@@ -283,3 +283,32 @@ def test_attention_backward(B, T, NH, hs):
     dqkv2 = torch.empty_like(dqkv)
     KN.attention_backward(dqkv2, dout.to(DEV), dev_qkv, out, lse, B, T, NH)
     assert torch.equal(dqkv, dqkv2)
+
+
+@pytest.mark.parametrize("M,N,K", [(512, 512, 128), (1024, 2304, 768), (300, 520, 320), (2048, 768, 3072)])
+def test_two_sm_gemm_forward_and_dgrad(M, N, K, monkeypatch):
+    """The cta_group::2 kernel (256 x 256 tiles on CTA pairs) against the fp32 reference, all of its epilogues."""
+    monkeypatch.setattr(KN, "TWO_SM_MIN_TILES", 1)
+    inp, w, b = rnd(M, K), rnd(N, K, scale=0.05), rnd(N)
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    KN.matmul_forward(out, inp.to(DEV), w.to(DEV), b.to(DEV))
+    ref = torch.empty(M, N)
+    R.matmul_forward(ref, inp, w, b)
+    close(out, ref, 2e-2, 1e-2, "2sm forward")
+    pre = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    KN.matmul_forward(out, inp.to(DEV), w.to(DEV), b.to(DEV), pre_gelu=pre)
+    refpre = torch.empty(M, N)
+    R.matmul_forward(ref, inp, w, b, pre_gelu=refpre)
+    close(pre, refpre, 2e-2, 1e-2, "2sm pre-gelu")
+    close(out, ref, 2e-2, 1e-2, "2sm gelu")
+    # dgrad: dinp[M,K] = dout[M,N] @ w[N,K] (B operand MN-major), with and without dGELU
+    dout = rnd(M, N, seed=3)
+    dinp = torch.empty(M, K, dtype=torch.bfloat16, device=DEV)
+    KN.matmul_dgrad(dinp, dout.to(DEV), w.to(DEV))
+    rd = torch.empty(M, K)
+    R.matmul_dgrad(rd, dout, w)
+    close(dinp, rd, 3e-2, 1e-2, "2sm dgrad")
+    pg = rnd(M, K, seed=5)
+    KN.matmul_dgrad(dinp, dout.to(DEV), w.to(DEV), pre_gelu=pg.to(DEV))
+    R.matmul_dgrad(rd, dout, w, pre_gelu=pg)
+    close(dinp, rd, 3e-2, 1e-2, "2sm dgrad+dgelu")
