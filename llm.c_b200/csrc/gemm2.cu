@@ -1,7 +1,7 @@
 // Two-SM bf16 GEMM for sm_100a: a cluster of two CTAs computes one 256 x 256 tile of D = A * B^T with
 // tcgen05.mma.cta_group::2.  Each CTA stages only its own half of both operands (128 rows of A, 128 rows of B per
 // 64-wide k-block: 32 KB per stage instead of the 48 KB a single-CTA 128 x 256 tile needs for the same FLOPs), so
-// L2 -> shared-memory traffic per FLOP drops by a third and six pipeline stages fit.  The MMA instruction, issued by
+// L2 -> shared-memory traffic per FLOP drops by a third and five pipeline stages fit next to 64 KB of epilogue staging.  The MMA instruction, issued by
 // the leader CTA, reads both CTAs' shared memory and writes each CTA's 128 accumulator rows into that CTA's TMEM.
 //
 // No TMA load uses cluster multicast: each CTA loads its own halves with plain `.cta_group::2` bulk tensor copies
@@ -10,7 +10,8 @@
 //
 // Supported: forward (A, B K-major; STORE + bias, GELU + pre-activation), dgrad (B MN-major; STORE, DGELU) and wgrad
 // (A, B MN-major; bf16 accumulate with deterministic split-K).  Small problems use the single-CTA kernel (gemm.cu).
-// Epilogue structure is that of gemm.cu (two groups of four warps per CTA, 64-byte-swizzled staging, TMA stores).
+// Epilogue: sixteen warps per CTA in four groups of four, each group owning 64 columns of the CTA's 128 x 256 half tile
+// (64-byte-swizzled staging, TMA stores).
 #include "common.cuh"
 
 namespace {
@@ -22,14 +23,16 @@ constexpr int BK = 64, UMMA_K = 16;
 constexpr int A_STAGE_BYTES = BM * BK * 2;            // 16 KB
 constexpr int B_STAGE_BYTES = BNH * BK * 2;           // 16 KB
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int EPI_GROUPS = 4;          // epilogue groups of four warps, each owning BN / EPI_GROUPS columns of the tile
+constexpr int GROUP_COLS = BN / EPI_GROUPS;
 constexpr int EPI_COLS = 32;
 constexpr int EPI_BUF_BYTES = BM * EPI_COLS * 2;      // 8 KB
-// Epilogues with two tensors per chunk (GELU: activation + pre-activation out; dGELU: pre-activation in + gradient out)
-// double-buffer both, paid for with one pipeline stage.
-__host__ __device__ constexpr int stages_for(int mode) { return (mode == 1 || mode == 2) ? 5 : 6; }
-__host__ __device__ constexpr int epi_bufs_for(int mode) { return (mode == 1 || mode == 2) ? 8 : 4; }
+// Staging: two 8 KB buffers per epilogue group next to five pipeline stages.  STORE alternates between them; the epilogues
+// with two tensors per chunk (GELU: activation + pre-activation out; dGELU: pre-activation in + gradient out) use one each.
+__host__ __device__ constexpr int stages_for(int mode) { return 5; }
+__host__ __device__ constexpr int epi_bufs_for(int mode) { return 2 * EPI_GROUPS; }
 __host__ __device__ constexpr int smem_for(int mode) { return stages_for(mode) * STAGE_BYTES + epi_bufs_for(mode) * EPI_BUF_BYTES + 1024 + 256; }
-constexpr int NUM_THREADS = 320;
+constexpr int NUM_THREADS = 576;       // TMA warp + MMA warp + 16 epilogue warps
 constexpr int TMEM_COLS = 512;
 constexpr int RASTER_GROUP = 8;       // in units of 256-row tiles
 
@@ -48,7 +51,7 @@ struct Gemm2Args {
     unsigned int* status;
 };
 
-DEVINL void epi_barrier() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+DEVINL void epi_barrier() { asm volatile("bar.sync 1, 512;" ::: "memory"); }
 
 DEVINL void group_barrier(int grp) { asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory"); }
 DEVINL bool epi_any(int pred) {
@@ -56,7 +59,7 @@ DEVINL bool epi_any(int pred) {
     asm volatile(
         "{\n\t.reg .pred p, q;\n\t"
         "setp.ne.u32 q, %1, 0;\n\t"
-        "bar.red.or.pred p, 1, 256, q;\n\t"
+        "bar.red.or.pred p, 1, 512, q;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}" : "=r"(r) : "r"(pred) : "memory");
     return r != 0;
 }
@@ -110,9 +113,9 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     uint64_t* full = bars;                    // [STAGES]  used in the leader CTA: bytes of both CTAs' loads
     uint64_t* empty = bars + STAGES;          // [STAGES]  one per CTA, raised by the leader's multicast commit
     uint64_t* acc_full = bars + 2 * STAGES;   // [2]       one per CTA, raised by the leader's multicast commit
-    uint64_t* acc_empty = acc_full + 2;       // [2]       used in the leader CTA: 16 epilogue warps of the pair
-    uint64_t* aux_full = acc_empty + 2;       // [2 groups][2 buffers]  (EPI_DGELU)
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aux_full + 4);
+    uint64_t* acc_empty = acc_full + 2;       // [2]       used in the leader CTA: all epilogue warps of the pair arrive
+    uint64_t* aux_full = acc_empty + 2;       // [EPI_GROUPS]  (EPI_DGELU)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aux_full + EPI_GROUPS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     int* last_flag = const_cast<int*>(abort_flag) + 1;
 
@@ -123,8 +126,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        for (int b = 0; b < 2; b++) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 16); }
-        for (int b = 0; b < 4; b++) mbar_init(&aux_full[b], 1);
+        for (int b = 0; b < 2; b++) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 2 * 4 * EPI_GROUPS); }
+        for (int b = 0; b < EPI_GROUPS; b++) mbar_init(&aux_full[b], 1);
         *abort_flag = 0;
         mbar_fence_init();
     }
@@ -222,26 +225,25 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
             }
         }
     } else {
-        // ---------------- epilogue (warps 2..9 of each CTA, on that CTA's 128 rows) ----------------
+        // ---------------- epilogue (warps 2..17 of each CTA, on that CTA's 128 rows) ----------------
         const int ew = warp - 2;
         const int grp = ew >> 2;
         const int q = warp & 3;
         const int row = q * 32 + lane;
         const bool leader = ((ew & 3) == 0) && lane == 0;
-        // staging buffers of this group: [pair p = chunk parity][0: D out, 1: aux (pre-activation out / in)]; STORE and ACCUM
-        // modes only have one pair and alternate between its two buffers
-        constexpr int BUFS_PER_GROUP = NUM_EPI_BUFS / 2;
+        // this group's two staging buffers
+        constexpr int BUFS_PER_GROUP = NUM_EPI_BUFS / EPI_GROUPS;
         uint8_t* gbuf = epi_smem + grp * BUFS_PER_GROUP * EPI_BUF_BYTES;
-        constexpr int CHUNKS = (BN / 2) / EPI_COLS;
+        constexpr int CHUNKS = GROUP_COLS / EPI_COLS;
         const int swz = (row >> 1) & 3;
         uint32_t kctr = 0;
         const bool store_thread = (threadIdx.x == 64);
-        // pre-activation chunk number k (counted per group over the whole kernel) -> aux buffer k & 1   (EPI_DGELU)
-        auto aux_load = [&](int w_, int c_, uint32_t k_) {
+        // pre-activation chunk -> this group's second buffer (EPI_DGELU); chunk k completes phase k & 1 of the group's barrier
+        auto aux_load = [&](int w_, int c_) {
             int mt_, nt_, sp_; decode(w_, mt_, nt_, sp_);
-            uint64_t* bar = &aux_full[grp * 2 + (k_ & 1)];
+            uint64_t* bar = &aux_full[grp];
             mbar_expect_tx(bar, EPI_BUF_BYTES);
-            tma_load_2d(gbuf + ((k_ & 1) * 2 + 1) * EPI_BUF_BYTES, &tmAux, bar, nt_ * BN + grp * (BN / 2) + c_ * EPI_COLS, mt_ * 256 + (int)rank * BM);
+            tma_load_2d(gbuf + EPI_BUF_BYTES, &tmAux, bar, nt_ * BN + grp * GROUP_COLS + c_ * EPI_COLS, mt_ * 256 + (int)rank * BM);
         };
         // (work item, chunk) that follows (w_, c_) in this group's sequence; false at the end
         auto next_chunk = [&](int& w_, int& c_) {
@@ -249,11 +251,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
             if (w_ + npairs < total_work) { w_ += npairs; c_ = 0; return true; }
             return false;
         };
-        if (MODE == EPI_DGELU && leader && pair < total_work) {      // prefetch distance: two chunks
-            int w_ = pair, c_ = 0;
-            aux_load(w_, c_, 0);
-            if (next_chunk(w_, c_)) aux_load(w_, c_, 1);
-        }
+        if (MODE == EPI_DGELU && leader && pair < total_work) aux_load(pair, 0);
         const uint32_t lead_acc_empty0 = map_to_cta(smem_u32(&acc_empty[0]), 0);
         const uint32_t lead_acc_empty1 = map_to_cta(smem_u32(&acc_empty[1]), 0);
         int it = 0;
@@ -263,9 +261,9 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
             const uint32_t use = (uint32_t)(it >> 1);
             bool ok = mbar_wait(&acc_full[buf], use & 1, abort_flag, g.status, 0xC00 + buf);
             tc_fence_after();
-            const int m0 = mt * 256 + (int)rank * BM, n0 = nt * BN + grp * (BN / 2);
+            const int m0 = mt * 256 + (int)rank * BM, n0 = nt * BN + grp * GROUP_COLS;
             const int grow = m0 + row;
-            const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + grp * (BN / 2);
+            const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + grp * GROUP_COLS;
             const uint32_t lead_acc_empty = buf ? lead_acc_empty1 : lead_acc_empty0;
             if (MODE == EPI_ACCUM) {
                 // ---- EPI_ACCUM: direct global read-modify-write, optional split-K ----
@@ -304,7 +302,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                 } else {
                     // partial tile -> workspace, laid out [col/4][row][4] so that a warp writes 512 contiguous bytes
                     float* wsp = g.workspace + ((size_t)tile * g.splits + sp) * (BM * BN);
-                    const int cbase = grp * (BN / 2);
+                    const int cbase = grp * GROUP_COLS;
                     #pragma unroll 1
                     for (int c = 0; c < CHUNKS; c++) {
                         uint32_t v[32];
@@ -332,7 +330,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                         const float* wt = g.workspace + (size_t)tile * g.splits * (BM * BN);
                         if (grow < g.M) {
                             #pragma unroll 1
-                            for (int jj = 0; jj < BN / 2; jj += 8) {
+                            for (int jj = 0; jj < GROUP_COLS; jj += 8) {
                                 const int j = cbase + jj;              // column inside the tile
                                 if (nt * BN + j >= g.N) break;
                                 float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -396,15 +394,16 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                 uint8_t* out_buf; uint8_t* aux_buf = nullptr;
                 if (MODE == EPI_STORE) {
                     out_buf = gbuf + (kctr & 1) * EPI_BUF_BYTES;
+                    if (leader) tma_store_wait_read<1>();      // the store issued two chunks ago has read this buffer
                 } else {
-                    out_buf = gbuf + ((kctr & 1) * 2 + 0) * EPI_BUF_BYTES;
-                    aux_buf = gbuf + ((kctr & 1) * 2 + 1) * EPI_BUF_BYTES;
+                    out_buf = gbuf;
+                    aux_buf = gbuf + EPI_BUF_BYTES;
+                    if (leader) tma_store_wait_read<0>();
                 }
                 uint8_t* out_row = out_buf + row * 64;
                 uint8_t* aux_row = aux_buf + row * 64;
-                if (leader) tma_store_wait_read<1>();      // the stores issued two chunks ago have read these buffers
                 if (MODE == EPI_DGELU) {
-                    ok = mbar_wait(&aux_full[grp * 2 + (kctr & 1)], (kctr >> 1) & 1, abort_flag, g.status, 0xC40 + grp) && ok;
+                    ok = mbar_wait(&aux_full[grp], kctr & 1, abort_flag, g.status, 0xC40 + grp) && ok;
                     #pragma unroll
                     for (int j = 0; j < 4; j++) {
                         const uint4 a = *reinterpret_cast<const uint4*>(aux_row + ((j ^ swz) * 16));
@@ -417,9 +416,9 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                 }
                 group_barrier(grp);      // output buffer is free; (DGELU) everybody has read this pre-activation chunk
                 if (MODE == EPI_DGELU && leader) {
-                    // refill the aux buffer just consumed with the chunk two positions ahead
+                    // refill the buffer just consumed with the next chunk's pre-activation
                     int w_ = w, c_ = c;
-                    if (next_chunk(w_, c_) && next_chunk(w_, c_)) aux_load(w_, c_, kctr + 2);
+                    if (next_chunk(w_, c_)) aux_load(w_, c_);
                 }
                 if (MODE == EPI_GELU) {
                     #pragma unroll
