@@ -53,7 +53,7 @@ def cuda():
         "llmc_layernorm_fwd": (I, [P, P, P, P, P, P, I, I, S]),
         "llmc_fused_residual_fwd": (I, [P, P, P, P, P, P, P, P, I, I, S]),
         "llmc_layernorm_bwd_scratch": (L, [I, I]),
-        "llmc_layernorm_bwd": (I, [P, P, P, P, P, P, P, P, P, I, I, I, I, S]),
+        "llmc_layernorm_bwd": (I, [P, P, P, P, P, P, P, P, P, I, I, I, I, P, I, S]),
         "llmc_encoder_fwd": (I, [P, P, P, P, I, I, I, I, S]),
         "llmc_encoder_bwd": (I, [P, P, P, P, I, I, I, I, I, I, U, S]),
         "llmc_fused_classifier": (I, [P, P, P, F, I, I, I, I, I, S]),

@@ -18,54 +18,63 @@ __global__ void __launch_bounds__(CLS_THREADS)
 classifier_kernel(bf16* __restrict__ logits, float* __restrict__ losses, const int* __restrict__ targets,
                   float dloss, int V, int Vp, int accumulate_loss) {
     __shared__ float red[32];
+    constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
     // rows are processed back to front so that the rows the LM-head GEMM wrote last (still in L2) go first
     const int row = gridDim.x - 1 - blockIdx.x;
     bf16* x = logits + (size_t)row * Vp;
     const int target = targets[row];
     const int vpack = V >> 3;                 // full packs of valid columns
+    // pass 1: running maximum and sum of 2^((x - max) * log2 e), per thread, one pack at a time
     float m = -INFINITY, s = 0.f;
     for (int p = threadIdx.x; p < vpack; p += CLS_THREADS) {
         bf16x8 a = ld128(x + p * 8);
+        float f[8];
         float mx = m;
         #pragma unroll
-        for (int e = 0; e < 8; e++) mx = fmaxf(mx, __bfloat162float(a[e]));
+        for (int e = 0; e < 8; e++) { f[e] = __bfloat162float(a[e]); mx = fmaxf(mx, f[e]); }
+        const float off = mx * LOG2E;
         float add = 0.f;
         #pragma unroll
-        for (int e = 0; e < 8; e++) add += __expf(__bfloat162float(a[e]) - mx);
-        s = s * __expf(m - mx) + add;
+        for (int e = 0; e < 8; e++) add += ex2_fast(fmaf(f[e], LOG2E, -off));
+        s = s * ex2_fast((m - mx) * LOG2E) + add;
         m = mx;
     }
     // ragged tail of valid columns (V not a multiple of 8)
     for (int c = vpack * 8 + threadIdx.x; c < V; c += CLS_THREADS) {
         float v = __bfloat162float(x[c]);
         float mx = fmaxf(m, v);
-        s = s * __expf(m - mx) + __expf(v - mx);
+        s = s * ex2_fast((m - mx) * LOG2E) + ex2_fast((v - mx) * LOG2E);
         m = mx;
     }
     const float gmax = block_max(m, red);
-    s = (m == -INFINITY) ? 0.f : s * __expf(m - gmax);
+    s = (m == -INFINITY) ? 0.f : s * ex2_fast((m - gmax) * LOG2E);
     const float gsum = block_sum(s, red);
-    const float inv = 1.0f / gsum;
 
     if (threadIdx.x == 0) {
         float lt = __bfloat162float(x[target]);
-        float loss = -(lt - gmax - logf(gsum));
+        float loss = -(lt - gmax - log2f(gsum) * LN2);
         if (accumulate_loss) losses[row] += loss; else losses[row] = loss;
     }
     if (!WRITE_DLOGITS) return;
     __syncthreads();    // the target logit has been read
+    // pass 2 (the row is still in L2): dlogits = (softmax - onehot) * dloss; the vocabulary padding becomes zero
+    const float goff = gmax * LOG2E;
+    const float k = dloss / gsum;
     const int ppack = Vp >> 3;
+    const int tpack = target >> 3;
     for (int p = threadIdx.x; p < ppack; p += CLS_THREADS) {
         bf16x8 a = ld128(x + p * 8);
-        bf16x8 o;
+        float g[8];
         #pragma unroll
-        for (int e = 0; e < 8; e++) {
-            const int c = p * 8 + e;
-            float prob = __expf(__bfloat162float(a[e]) - gmax) * inv;
-            float g = (prob - (c == target ? 1.0f : 0.0f)) * dloss;
-            o[e] = (c < V) ? __float2bfloat16_rn(g) : __float2bfloat16_rn(0.f);
+        for (int e = 0; e < 8; e++) g[e] = ex2_fast(fmaf(__bfloat162float(a[e]), LOG2E, -goff)) * k;
+        if (p == tpack) g[target & 7] -= dloss;
+        if (p >= vpack) {                      // the pack that straddles V, and the padding
+            #pragma unroll
+            for (int e = 0; e < 8; e++) if (p * 8 + e >= V) g[e] = 0.f;
         }
-        st128cs(x + p * 8, o);
+        uint4 o;
+        o.x = pack_bf16x2(g[0], g[1]); o.y = pack_bf16x2(g[2], g[3]); o.z = pack_bf16x2(g[4], g[5]); o.w = pack_bf16x2(g[6], g[7]);
+        __stcs(reinterpret_cast<uint4*>(x + p * 8), o);
     }
 }
 

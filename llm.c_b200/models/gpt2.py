@@ -284,8 +284,10 @@ class GPT:
 
         ops.matmul_dgrad(dl_btc, dlogits, p["wte"])
         ops.matmul_wgrad(g["wte"], dlogits, a["lnf"], accumulate=acc)
+        # every LayerNorm backward also emits the column sums of the residual-stream gradient it leaves behind: that is the
+        # bias gradient of the projection (fcproj / attproj) whose output was added to the stream just before that LayerNorm
         ops.layernorm_backward(dres, g["lnfw"], g["lnfb"], dl_btc, a["residual3"][L - 1], p["lnfw"], a["lnf_mean"], a["lnf_rstd"],
-                               accumulate_dinp=False, accumulate_dwdb=acc)
+                               accumulate_dinp=False, accumulate_dwdb=acc, dcolsum=g["fcprojb"][L - 1], accumulate_dcol=acc)
         nvtx = self.device.type == "cuda"
         for l in reversed(range(L)):
           with _Range("backward layer %d" % l, nvtx):
@@ -294,7 +296,6 @@ class GPT:
             lg = 0 if self.recompute >= 1 else l
             if self.recompute >= 1:
                 ops.gelu_forward(a["fch_gelu"][lg], a["fch"][l])
-            ops.bias_grad(g["fcprojb"][l], dres, accumulate=acc)
             ops.matmul_dgrad(dl_bt4c, dres, p["fcprojw"][l], pre_gelu=a["fch"][l])
             ops.matmul_wgrad(g["fcprojw"][l], dres, a["fch_gelu"][lg], accumulate=acc)
             if self.recompute >= 2:
@@ -303,8 +304,7 @@ class GPT:
             ops.matmul_dgrad(dl_btc, dl_bt4c, p["fcw"][l])
             ops.matmul_wgrad(g["fcw"][l], dl_bt4c, a["ln2"][lln], accumulate=acc)
             ops.layernorm_backward(dres, g["ln2w"][l], g["ln2b"][l], dl_btc, a["residual2"][l], p["ln2w"][l], a["ln2_mean"][l],
-                                   a["ln2_rstd"][l], accumulate_dinp=True, accumulate_dwdb=acc)
-            ops.bias_grad(g["attprojb"][l], dres, accumulate=acc)
+                                   a["ln2_rstd"][l], accumulate_dinp=True, accumulate_dwdb=acc, dcolsum=g["attprojb"][l], accumulate_dcol=acc)
             ops.matmul_dgrad(dl_btc, dres, p["attprojw"][l])
             ops.matmul_wgrad(g["attprojw"][l], dres, a["atty"][l], accumulate=acc)
             ops.attention_backward(dqkv, dl_btc, a["qkv"][l], a["atty"][l], a["lse"][l], B, T, NH)
@@ -314,7 +314,8 @@ class GPT:
             ops.matmul_dgrad(dl_btc, dqkv, p["qkvw"][l])
             ops.matmul_wgrad(g["qkvw"][l], dqkv, a["ln1"][lln], accumulate=acc)
             ops.layernorm_backward(dres, g["ln1w"][l], g["ln1b"][l], dl_btc, residual, p["ln1w"][l], a["ln1_mean"][l],
-                                   a["ln1_rstd"][l], accumulate_dinp=True, accumulate_dwdb=acc)
+                                   a["ln1_rstd"][l], accumulate_dinp=True, accumulate_dwdb=acc,
+                                   dcolsum=(g["fcprojb"][l - 1] if l > 0 else None), accumulate_dcol=acc)
             if hook is not None:
                 hook(l)
         ops.encoder_backward(g["wte"], g["wpe"][:T], dres.view(B, T, C), self.inputs, accumulate_wte=True, accumulate_wpe=acc,

@@ -156,15 +156,21 @@ def fused_residual_forward(residual, normed, mean, rstd, inp1, inp2, weight, bia
                                               _p(bias), N, C, _stream()), "llmc_fused_residual_fwd")
 
 
-def layernorm_backward(dinp, dweight, dbias, dout, inp, weight, mean, rstd, accumulate_dinp=True, accumulate_dwdb=True):
-    """dinp (+)= dLN(dout); dweight/dbias (+)= their gradients."""
+def layernorm_backward(dinp, dweight, dbias, dout, inp, weight, mean, rstd, accumulate_dinp=True, accumulate_dwdb=True,
+                       dcolsum=None, accumulate_dcol=True):
+    """dinp (+)= dLN(dout); dweight/dbias (+)= their gradients.  ``dcolsum`` (+)= column sums of the final dinp: the bias
+    gradient of the projection that wrote into the residual stream, at no extra pass over memory."""
     global _launches
     lib = _lib.cuda()
     N, C = inp.shape
     s = _scratch.get("ln_bwd", lib.llmc_layernorm_bwd_scratch(N, C), torch.float32, inp.device)
+    fused_col = dcolsum is not None and C <= 1024
     _launches += 2
     check(lib.llmc_layernorm_bwd(_p(dinp), _p(dweight), _p(dbias), _p(s), _p(dout), _p(inp), _p(weight), _p(mean), _p(rstd),
-                                 N, C, int(accumulate_dinp), int(accumulate_dwdb), _stream()), "llmc_layernorm_bwd")
+                                 N, C, int(accumulate_dinp), int(accumulate_dwdb), _p(dcolsum if fused_col else None),
+                                 int(accumulate_dcol), _stream()), "llmc_layernorm_bwd")
+    if dcolsum is not None and not fused_col:
+        bias_grad(dcolsum, dinp, accumulate=accumulate_dcol)
 
 
 def attention_forward(out, lse, qkv, B, T, NH):

@@ -96,7 +96,8 @@ def fused_residual_forward(residual, normed, mean, rstd, inp1, inp2, weight, bia
     layernorm_forward(normed, mean, rstd, residual, weight, bias)
 
 
-def layernorm_backward(dinp, dweight, dbias, dout, inp, weight, mean, rstd, accumulate_dinp=True, accumulate_dwdb=True):
+def layernorm_backward(dinp, dweight, dbias, dout, inp, weight, mean, rstd, accumulate_dinp=True, accumulate_dwdb=True,
+                       dcolsum=None, accumulate_dcol=True):
     dy, x, w = _f(dout), _f(inp), _f(weight)
     norm = (x - mean.unsqueeze(-1)) * rstd.unsqueeze(-1)
     dnorm = dy * w
@@ -110,6 +111,11 @@ def layernorm_backward(dinp, dweight, dbias, dout, inp, weight, mean, rstd, accu
     dinp.copy_(dx)
     dweight.copy_(dw)
     dbias.copy_(db)
+    if dcolsum is not None:
+        cs = _f(dinp).sum(0)
+        if accumulate_dcol:
+            cs = cs + _f(dcolsum)
+        dcolsum.copy_(cs)
 
 
 def _split_qkv(qkv, B, T, NH):

@@ -131,6 +131,14 @@ def test_layernorm_forward_backward(N, C):
     dx2, dw2, db2 = dx0.to(DEV).clone(), dw0.to(DEV).clone(), db0.to(DEV).clone()
     KN.layernorm_backward(dx2, dw2, db2, dy.to(DEV), x.to(DEV), w.to(DEV), mean, rstd, True, True)
     assert torch.equal(dw, dw2) and torch.equal(db, db2) and torch.equal(dx, dx2)
+    # fused column sums of the final dinp (the bias gradient of the residual projection), fresh and accumulated
+    for acc_col in (False, True):
+        dx3, dw3, db3, dc0 = dx0.to(DEV).clone(), dw0.to(DEV).clone(), db0.to(DEV).clone(), rnd(C, seed=21)
+        dc = dc0.to(DEV).clone()
+        KN.layernorm_backward(dx3, dw3, db3, dy.to(DEV), x.to(DEV), w.to(DEV), mean, rstd, True, True, dcolsum=dc, accumulate_dcol=acc_col)
+        assert torch.equal(dx3, dx) and torch.equal(dw3, dw)
+        want = dx.float().cpu().sum(0) + (dc0.float() if acc_col else 0.0)
+        close(dc, want, 0.2, 2e-2, "ln dcolsum")
 
 
 def test_fused_residual_forward():
