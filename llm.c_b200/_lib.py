@@ -58,6 +58,14 @@ def cuda():
         "llmc_encoder_bwd": (I, [P, P, P, P, I, I, I, I, I, I, U, S]),
         "llmc_fused_classifier": (I, [P, P, P, F, I, I, I, I, I, S]),
         "llmc_gelu_fwd": (I, [P, P, L, S]),
+        "llmc_rmsnorm_fwd": (I, [P, P, P, P, I, I, F, S]),
+        "llmc_rmsnorm_fused_residual_fwd": (I, [P, P, P, P, P, P, I, I, F, S]),
+        "llmc_rmsnorm_bwd_scratch": (L, [I, I]),
+        "llmc_rmsnorm_bwd": (I, [P, P, P, P, P, P, P, I, I, I, I, S]),
+        "llmc_rope_fwd": (I, [P, P, P, L, I, I, I, I, S]),
+        "llmc_rope_bwd": (I, [P, P, P, L, I, I, I, I, S]),
+        "llmc_swiglu_fwd": (I, [P, P, L, I, S]),
+        "llmc_swiglu_bwd": (I, [P, P, P, L, I, S]),
         "llmc_gelu_bwd_inplace": (I, [P, P, L, S]),
         "llmc_residual_add": (I, [P, P, P, L, S]),
         "llmc_bias_grad_scratch": (L, [I, I]),

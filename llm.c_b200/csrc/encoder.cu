@@ -23,6 +23,10 @@ __global__ void encoder_fwd_kernel(bf16* __restrict__ out, const int* __restrict
     const int t = (int)(bt % T);
     const int tok = min(max(tokens[bt], 0), V - 1);      // ids are validated on the host; never index outside the table
     bf16x8 a = ld128(wte + (size_t)tok * C + p * 8);
+    if (wpe == nullptr) {                                // models with rotary positions have no position table
+        st128cs(out + bt * C + p * 8, a);
+        return;
+    }
     bf16x8 b = ld128(wpe + (size_t)t * C + p * 8);
     bf16x8 o;
     #pragma unroll
@@ -182,8 +186,10 @@ extern "C" int llmc_encoder_fwd(bf16* out, const int* tokens, const bf16* wte, c
 extern "C" int llmc_encoder_bwd(bf16* dwte, bf16* dwpe, const bf16* dout, const int* tokens, int B, int T, int C, int V,
                                 int accumulate_wte, int accumulate_wpe, unsigned int seed, cudaStream_t stream) {
     if (C % 8) return -1;
-    wpe_bwd_kernel<<<CEIL_DIV(T * (C / 8), 256), 256, 0, stream>>>(dwpe, dout, B, T, C, accumulate_wpe, seed);
-    CUDA_CHECK(cudaGetLastError());
+    if (dwpe != nullptr) {
+        wpe_bwd_kernel<<<CEIL_DIV(T * (C / 8), 256), 256, 0, stream>>>(dwpe, dout, B, T, C, accumulate_wpe, seed);
+        CUDA_CHECK(cudaGetLastError());
+    }
     wte_bwd_kernel<<<CEIL_DIV(V, IDS_PER_CTA), WTE_THREADS, 0, stream>>>(dwte, dout, tokens, B * T, C, V, accumulate_wte, seed + 1);
     CUDA_CHECK(cudaGetLastError());
     return 0;

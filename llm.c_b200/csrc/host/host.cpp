@@ -119,7 +119,8 @@ API void llmc_rng_get_state(void* p, void* out) { memcpy(out, p, sizeof(MTState)
 API void llmc_rng_set_state(void* p, const void* in) { memcpy(p, in, sizeof(MTState)); }
 
 // ---------------------------------------------------------------------------------------------
-// token shards: 256 x int32 header {20240520, 1, ntok}, then ntok x uint16
+// token shards: 256 x int32 header {20240520, 1, ntok} then ntok x uint16 (GPT-2 vocabulary), or
+// {20240801, 7, ntok} then ntok x uint32 (LLaMA-3 vocabulary, which does not fit 16 bits)
 
 struct Shard {
     std::string path;
@@ -142,23 +143,31 @@ struct MappedFile {
     }
 };
 
-static int read_shard_header(const std::string& path, int64_t* ntok) {
+static int read_shard_header(const std::string& path, int64_t* ntok, size_t* tok_bytes) {
     FILE* f = fopen(path.c_str(), "rb");
     if (!f) return fail("cannot open " + path);
     int header[256];
     if (fread(header, sizeof(int), 256, f) != 256) { fclose(f); return fail("short header in " + path); }
     fseek(f, 0, SEEK_END); int64_t size = ftell(f); fclose(f);
-    if (header[0] != 20240520) return fail("bad magic in token shard " + path);
-    if (header[1] != 1) return fail("bad version in token shard " + path);
+    if (header[0] == 20240520) {
+        if (header[1] != 1) return fail("bad version in token shard " + path);
+        *tok_bytes = sizeof(uint16_t);
+    } else if (header[0] == 20240801) {
+        if (header[1] != 7) return fail("bad version in token shard " + path);
+        *tok_bytes = sizeof(uint32_t);
+    } else {
+        return fail("bad magic in token shard " + path);
+    }
     *ntok = header[2];
     if (*ntok <= 0) return fail("empty token shard " + path);
-    if (size != (int64_t)(256 * sizeof(int)) + *ntok * (int64_t)sizeof(uint16_t)) return fail("size of " + path + " does not match its header");
+    if (size != (int64_t)(256 * sizeof(int)) + *ntok * (int64_t)*tok_bytes) return fail("size of " + path + " does not match its header");
     return 0;
 }
 
 struct DataLoader {
     int rank = 0, nproc = 1, shuffle = 0;
     size_t B = 0, T = 0;
+    size_t tok_bytes = sizeof(uint16_t);      // width of a token in the shard files (all shards of a loader agree)
     std::vector<Shard> shards;
     int64_t num_tokens = 0;
     size_t shard_num_samples = 0, current_shard = 0, current_sample = 0;
@@ -173,8 +182,8 @@ struct DataLoader {
     int load_shard(size_t idx) {
         size_t real = shuffle ? (size_t)shard_indices[idx] : idx;
         if (file.open_(shards[real].path)) return -1;
-        size_t total_batch_bytes = (size_t)nproc * B * T * sizeof(uint16_t);
-        shard_num_samples = ((size_t)shards[real].ntok * sizeof(uint16_t) - sizeof(uint16_t)) / total_batch_bytes;
+        size_t total_batch_bytes = (size_t)nproc * B * T * tok_bytes;
+        shard_num_samples = ((size_t)shards[real].ntok * tok_bytes - tok_bytes) / total_batch_bytes;
         return 0;
     }
     void prepare_intra() {
@@ -200,13 +209,18 @@ struct DataLoader {
     int next(int* inputs, int* targets) {
         if (current_sample >= shard_num_samples) { if (advance()) return -1; }
         size_t idx = shuffle ? (size_t)intra_indices[current_sample] : current_sample;
-        size_t total_batch_bytes = (size_t)nproc * B * T * sizeof(uint16_t);
-        size_t off = 256 * sizeof(int) + idx * total_batch_bytes + (size_t)rank * B * T * sizeof(uint16_t);
-        size_t need = (B * T + 1) * sizeof(uint16_t);
+        size_t total_batch_bytes = (size_t)nproc * B * T * tok_bytes;
+        size_t off = 256 * sizeof(int) + idx * total_batch_bytes + (size_t)rank * B * T * tok_bytes;
+        size_t need = (B * T + 1) * tok_bytes;
         if (off + need > file.size) return fail("batch reaches past the end of the shard");
-        const uint16_t* src = (const uint16_t*)(file.base + off);
         const size_t n = B * T;
-        for (size_t i = 0; i < n; i++) { inputs[i] = (int)src[i]; targets[i] = (int)src[i + 1]; }
+        if (tok_bytes == sizeof(uint16_t)) {
+            const uint16_t* src = (const uint16_t*)(file.base + off);
+            for (size_t i = 0; i < n; i++) { inputs[i] = (int)src[i]; targets[i] = (int)src[i + 1]; }
+        } else {
+            const uint32_t* src = (const uint32_t*)(file.base + off);
+            for (size_t i = 0; i < n; i++) { inputs[i] = (int)src[i]; targets[i] = (int)src[i + 1]; }
+        }
         current_sample += 1;
         return 0;
     }
@@ -232,7 +246,10 @@ API void* llmc_dl_new(const char* pattern, long long B, long long T, int rank, i
     dl->rank = rank; dl->nproc = nproc; dl->shuffle = shuffle; dl->B = (size_t)B; dl->T = (size_t)T;
     for (size_t i = 0; i < g.gl_pathc; i++) {
         Shard s; s.path = g.gl_pathv[i];
-        if (read_shard_header(s.path, &s.ntok)) { globfree(&g); delete dl; return nullptr; }
+        size_t width = 0;
+        if (read_shard_header(s.path, &s.ntok, &width)) { globfree(&g); delete dl; return nullptr; }
+        if (i > 0 && width != dl->tok_bytes) { fail("shards of one pattern mix 16-bit and 32-bit tokens"); globfree(&g); delete dl; return nullptr; }
+        dl->tok_bytes = width;
         if (s.ntok < (int64_t)((size_t)nproc * B * T + 1)) { fail("shard " + s.path + " holds fewer tokens than one global batch"); globfree(&g); delete dl; return nullptr; }
         dl->num_tokens += s.ntok;
         dl->shards.push_back(s);

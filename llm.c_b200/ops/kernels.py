@@ -218,6 +218,69 @@ def residual_add(out, a, b):
     check(_lib.cuda().llmc_residual_add(_p(out), _p(a), _p(b), a.numel(), _stream()), "llmc_residual_add")
 
 
+def rmsnorm_forward(out, rstd, inp, weight, eps=1e-5):
+    """out = inp * rsqrt(mean(inp^2) + eps) * weight, statistics in fp32 (reference module: train_llama3.py:133-146)."""
+    global _launches
+    N, C = inp.shape
+    _launches += 1
+    check(_lib.cuda().llmc_rmsnorm_fwd(_p(out), _p(rstd), _p(inp), _p(weight), N, C, float(eps), _stream()), "llmc_rmsnorm_fwd")
+
+
+def rmsnorm_fused_residual_forward(residual, normed, rstd, inp1, inp2, weight, eps=1e-5):
+    """residual = inp1 + inp2; normed = RMSNorm(residual)."""
+    global _launches
+    N, C = inp1.shape
+    _launches += 1
+    check(_lib.cuda().llmc_rmsnorm_fused_residual_fwd(_p(residual), _p(normed), _p(rstd), _p(inp1), _p(inp2), _p(weight), N, C,
+                                                      float(eps), _stream()), "llmc_rmsnorm_fused_residual_fwd")
+
+
+def rmsnorm_backward(dinp, dweight, dout, inp, weight, rstd, accumulate_dinp=True, accumulate_dw=True):
+    """dinp (+)= dRMSNorm(dout); dweight (+)= its gradient."""
+    global _launches
+    lib = _lib.cuda()
+    N, C = inp.shape
+    s = _scratch.get("rms_bwd", lib.llmc_rmsnorm_bwd_scratch(N, C), torch.float32, inp.device)
+    _launches += 2
+    check(lib.llmc_rmsnorm_bwd(_p(dinp), _p(dweight), _p(s), _p(dout), _p(inp), _p(weight), _p(rstd), N, C, int(accumulate_dinp),
+                               int(accumulate_dw), _stream()), "llmc_rmsnorm_bwd")
+
+
+def rope_forward(packed, raw, freqs, T, NH, NKV):
+    """raw (N, (NH + 2 NKV) * HS) -> packed (N, 3, NH, HS): rotary embedding on queries and keys, key / value heads repeated
+    NH / NKV times (reference: apply_rotary_emb + repeat_kv, train_llama3.py:107-117 and :59-68).  freqs: (maxT, HS/2, 2) fp32."""
+    global _launches
+    N = raw.shape[0]
+    HS = raw.shape[1] // (NH + 2 * NKV)
+    _launches += 1
+    check(_lib.cuda().llmc_rope_fwd(_p(packed), _p(raw), _p(freqs), N, T, NH, NKV, HS, _stream()), "llmc_rope_fwd")
+
+
+def rope_backward(draw, dpacked, freqs, T, NH, NKV):
+    """Gradient of ``rope_forward``: inverse rotation, gradients of repeated heads summed over their group."""
+    global _launches
+    N = draw.shape[0]
+    HS = draw.shape[1] // (NH + 2 * NKV)
+    _launches += 1
+    check(_lib.cuda().llmc_rope_bwd(_p(draw), _p(dpacked), _p(freqs), N, T, NH, NKV, HS, _stream()), "llmc_rope_bwd")
+
+
+def swiglu_forward(h, x12):
+    """h = x12[:, :H] * silu(x12[:, H:])."""
+    global _launches
+    N, H = h.shape
+    _launches += 1
+    check(_lib.cuda().llmc_swiglu_fwd(_p(h), _p(x12), N, H, _stream()), "llmc_swiglu_fwd")
+
+
+def swiglu_backward(dx12, dh, x12):
+    """dx12 = gradient of ``swiglu_forward`` with respect to both halves of x12."""
+    global _launches
+    N, H = dh.shape
+    _launches += 1
+    check(_lib.cuda().llmc_swiglu_bwd(_p(dx12), _p(dh), _p(x12), N, H, _stream()), "llmc_swiglu_bwd")
+
+
 def make_table(views):
     """views: list of dicts(p_base, p_stride, o_base, o_stride, n, L, wd, seed)."""
     tab = TensorTable()

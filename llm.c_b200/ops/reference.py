@@ -57,17 +57,21 @@ def bias_grad(dbias, dout, accumulate=True):
 
 def encoder_forward(out, tokens, wte, wpe):
     B, T = tokens.shape
-    out.copy_((_f(wte)[tokens.long()] + _f(wpe)[:T].unsqueeze(0)).view_as(out))
+    x = _f(wte)[tokens.long()]
+    if wpe is not None:
+        x = x + _f(wpe)[:T].unsqueeze(0)
+    out.copy_(x.view_as(out))
 
 
 def encoder_backward(dwte, dwpe, dout, tokens, accumulate_wte=True, accumulate_wpe=True, seed=0):
     B, T = tokens.shape
     C = dwte.shape[1]
     d = _f(dout).view(B, T, C)
-    gp = d.sum(0)
-    if accumulate_wpe:
-        gp = gp + _f(dwpe[:T])
-    dwpe[:T].copy_(gp)
+    if dwpe is not None:
+        gp = d.sum(0)
+        if accumulate_wpe:
+            gp = gp + _f(dwpe[:T])
+        dwpe[:T].copy_(gp)
     gw = torch.zeros(dwte.shape, dtype=torch.float32)
     gw.index_add_(0, tokens.reshape(-1).long(), d.reshape(B * T, C))
     if accumulate_wte:
@@ -228,3 +232,86 @@ def master_from_params(master, params, views):
     for tv in views:
         for pb, ob, n in _view_slices(tv):
             master[ob:ob + n].copy_(_f(params[pb:pb + n]))
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# LLaMA-3 family operators
+
+def rmsnorm_forward(out, rstd, inp, weight, eps=1e-5):
+    x = _f(inp)
+    rs = torch.rsqrt(x.pow(2).mean(-1) + eps)
+    n = (x * rs.unsqueeze(-1)).to(out.dtype)          # rounded to the activation type before the weight is applied
+    out.copy_(_f(n) * _f(weight))
+    if rstd is not None:
+        rstd.copy_(rs)
+
+
+def rmsnorm_fused_residual_forward(residual, normed, rstd, inp1, inp2, weight, eps=1e-5):
+    residual.copy_(_f(inp1) + _f(inp2))
+    rmsnorm_forward(normed, rstd, residual, weight, eps)
+
+
+def rmsnorm_backward(dinp, dweight, dout, inp, weight, rstd, accumulate_dinp=True, accumulate_dw=True):
+    x, dy, w, rs = _f(inp), _f(dout), _f(weight), _f(rstd).unsqueeze(-1)
+    n = x * rs
+    dn = dy * w
+    dx = (dn - n * (dn * n).mean(-1, keepdim=True)) * rs
+    dw = (dy * n).sum(0)
+    if accumulate_dinp:
+        dx = dx + _f(dinp)
+    if accumulate_dw:
+        dw = dw + _f(dweight)
+    dinp.copy_(dx)
+    dweight.copy_(dw)
+
+
+def _rotate(x, freqs, T, sign):
+    """x (N, heads, HS) rotated pairwise by the angles of freqs (maxT, HS/2, 2) at position n % T."""
+    N, heads, HS = x.shape
+    f = _f(freqs)[:T].repeat(N // T, 1, 1)                      # (N, HS/2, 2)
+    c, s = f[..., 0].unsqueeze(1), f[..., 1].unsqueeze(1) * sign
+    re, im = x[..., 0::2], x[..., 1::2]
+    out = torch.empty_like(x)
+    out[..., 0::2] = re * c - im * s
+    out[..., 1::2] = re * s + im * c
+    return out
+
+
+def rope_forward(packed, raw, freqs, T, NH, NKV):
+    N = raw.shape[0]
+    HS = raw.shape[1] // (NH + 2 * NKV)
+    rep = NH // NKV
+    x = _f(raw).view(N, NH + 2 * NKV, HS)
+    q = _rotate(x[:, :NH], freqs, T, 1.0).to(packed.dtype)
+    k = _rotate(x[:, NH:NH + NKV], freqs, T, 1.0).to(packed.dtype)
+    v = x[:, NH + NKV:].to(packed.dtype)
+    out = packed.view(N, 3, NH, HS)
+    out[:, 0].copy_(q)
+    out[:, 1].copy_(k.repeat_interleave(rep, dim=1))
+    out[:, 2].copy_(v.repeat_interleave(rep, dim=1))
+
+
+def rope_backward(draw, dpacked, freqs, T, NH, NKV):
+    N = draw.shape[0]
+    HS = draw.shape[1] // (NH + 2 * NKV)
+    rep = NH // NKV
+    d = _f(dpacked).view(N, 3, NH, HS)
+    dq = _rotate(d[:, 0], freqs, T, -1.0)
+    dk = _rotate(d[:, 1].reshape(N, NKV, rep, HS).sum(2), freqs, T, -1.0)
+    dv = d[:, 2].reshape(N, NKV, rep, HS).sum(2)
+    draw.copy_(torch.cat([dq, dk, dv], dim=1).view(N, -1))
+
+
+def swiglu_forward(h, x12):
+    H = h.shape[1]
+    x = _f(x12)
+    h.copy_(x[:, :H] * torch.nn.functional.silu(x[:, H:]))
+
+
+def swiglu_backward(dx12, dh, x12):
+    H = dh.shape[1]
+    x, dy = _f(x12), _f(dh)
+    x1, x2 = x[:, :H], x[:, H:]
+    sg = torch.sigmoid(x2)
+    dx12[:, :H].copy_(dy * x2 * sg)
+    dx12[:, H:].copy_(dy * x1 * sg * (1.0 + x2 * (1.0 - sg)))

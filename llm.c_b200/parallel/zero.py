@@ -153,7 +153,7 @@ class ShardedAdamW:
         out = []
         for i, b in enumerate(self.base_views):
             v = dict(b)
-            v["wd"] = weight_decay if b["name"] in DECAYED else 0.0
+            v["wd"] = weight_decay if b["name"] in getattr(self.model, "decayed", DECAYED) else 0.0
             v["seed"] = seeds[i] if seeds is not None else 0
             out.append(v)
         return out

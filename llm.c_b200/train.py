@@ -16,7 +16,7 @@ from dataclasses import dataclass, field
 import torch
 
 from . import ops
-from .models import gpt2
+from .models import gpt2, llama3
 from .parallel import dist as pdist
 from .parallel.zero import ShardedAdamW
 from .utils import checkpoint, mfu
@@ -31,7 +31,8 @@ USAGE = """Usage:   python train_gpt2.py [options]
 Options (same letters as the reference trainer):
   -i <str>   train data filename pattern (default dev/data/tinyshakespeare/tiny_shakespeare_train.bin)
   -j <str>   val data filename pattern
-  -e <str>   model checkpoint .bin, or a descriptor dN | gpt2:dN | gpt3:cN for random init (default gpt2_124M_bf16.bin)
+  -e <str>   model checkpoint .bin (GPT-2/3 or LLaMA-3 file), or a descriptor dN | gpt2:dN | gpt3:cN | llama3:8B | llama3:l=..,c=..
+             for random init (default gpt2_124M_bf16.bin)
   -lg <int>  log GPU telemetry every N steps (default -1: never)
   -o <str>   output log dir (default: none, no logging / checkpoints)
   -n <int>   write checkpoints every N steps (default 0: never)   -nk <int> keep the last K   -nm <int> never delete multiples of M
@@ -180,8 +181,13 @@ class Trainer:
                     return sym_bufs[kind][0]
         if load.endswith(".bin"):
             mcfg, _ = checkpoint.read_model_header(load)
-            self.model = gpt2.GPT(mcfg, self.device, dtype, recompute=c.recompute, flat_allocator=allocator)
+            cls = llama3.Llama if checkpoint.model_family(load) == "llama3" else gpt2.GPT
+            self.model = cls(mcfg, self.device, dtype, recompute=c.recompute, flat_allocator=allocator)
             checkpoint.load_model(load, self.model)
+        elif load.startswith("llama3:"):
+            self.model = llama3.Llama(llama3.config_from_descriptor(load), self.device, dtype, recompute=c.recompute,
+                                      flat_allocator=allocator)
+            self.model.init_random(42)
         else:
             self.model = gpt2.GPT(gpt2.config_from_descriptor(load), self.device, dtype, recompute=c.recompute, flat_allocator=allocator)
             self.model.init_random(42)
@@ -338,8 +344,8 @@ class Trainer:
         """Autoregressive sampling on rank 0 (full prefix recomputed per token, as in the reference train_gpt2.cu:1752-1796)."""
         m = self.model
         if self._sample_model is None:
-            sm = gpt2.GPT(m.cfg, self.device, m.dtype, recompute=2)
-            sm.params_flat, sm.params = m.params_flat, m.params
+            # a second model object over the same parameter buffer, with its own (small) activation set
+            sm = type(m)(m.cfg, self.device, m.dtype, recompute=2, flat_allocator=lambda kind, numel, dt: m.params_flat)
             self._sample_model = sm
         sm = self._sample_model
         eot = min(self.tokenizer.eot_token, m.cfg.vocab_size - 1)
@@ -347,7 +353,7 @@ class Trainer:
         chunk = min(self.cfg.T, 256)
         tokens = torch.full((1, Tmax), eot, dtype=torch.int32)
         out = []
-        for t in range(1, genT):
+        for t in range(1, min(genT, m.cfg.max_seq_len + 1)):      # the context window bounds the generation
             Tcur = min(m.cfg.max_seq_len, -(-t // chunk) * chunk)
             dev_tokens = torch.full((1, Tcur), eot, dtype=torch.int32)
             dev_tokens[0, :min(t, Tcur)] = tokens[0, :min(t, Tcur)]

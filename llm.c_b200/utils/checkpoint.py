@@ -7,6 +7,13 @@
                         if shuffling: n_shards, shard_indices, n_samples, intra_shard_indices, raw mt19937 state
   DONE_%08d             empty marker, written by rank 0 once every rank has finished writing
 
+LLaMA-3 models use the reference's own header and tensor order (train_llama3.py:851-905 of the reference):
+  header {20240803, 3 | 5, block_size, vocab_size, n_layer, n_head, n_kv_head, n_embd, int(ffn_dim_multiplier), multiple_of,
+  int(norm_eps), int(rope_theta), use_scaled_rope, max_gen_batch_size, version major, version minor}; tensors wte, ln_1, c_attn,
+  attn c_proj, ln_2, c_fc, c_fc2, mlp c_proj, ln_f, lm_head, each stacked over layers.  The reference's writer truncates the
+  three float fields to integers; this writer also stores them exactly, as three float64 in header[17:23] (marker 1 in
+  header[16]), and the padded vocabulary in header[23]; the reference's readers ignore those slots.
+
 Device tensors are streamed through a bounded pinned staging buffer, so writing a checkpoint needs no host copy of
 the whole model.
 """
@@ -19,7 +26,7 @@ import torch
 
 from ..models.gpt2 import GPTConfig
 
-MODEL_MAGIC, STATE_MAGIC = 20240326, 20240527
+MODEL_MAGIC, STATE_MAGIC, LLAMA_MAGIC = 20240326, 20240527, 20240803
 CHUNK_ELEMS = 16 * 1024 * 1024
 
 
@@ -47,6 +54,8 @@ def _stream_in(f, t):
 
 
 def write_model(path, model):
+    if getattr(model, "family", "gpt2") == "llama3":
+        return _write_llama(path, model)
     cfg = model.cfg
     header = np.zeros(256, dtype=np.int32)
     version = 5 if model.dtype == torch.bfloat16 else 3
@@ -57,9 +66,20 @@ def write_model(path, model):
         _stream_out(f, model.params_flat)
 
 
+def model_family(path):
+    """'gpt2' or 'llama3', from the magic number of a model file."""
+    with open(path, "rb") as f:
+        magic = np.frombuffer(f.read(4), dtype=np.int32)
+    if magic.size == 1 and magic[0] == LLAMA_MAGIC:
+        return "llama3"
+    return "gpt2"
+
+
 def read_model_header(path):
     with open(path, "rb") as f:
         header = np.frombuffer(f.read(1024), dtype=np.int32)
+    if header.size == 256 and header[0] == LLAMA_MAGIC:
+        return _read_llama_header(header, path)
     if header.size != 256 or header[0] != MODEL_MAGIC:
         raise ValueError("bad magic in model file %s" % path)
     if header[1] not in (3, 5):
@@ -74,6 +94,8 @@ def load_model(path, model):
     if cfg != model.cfg:
         raise ValueError("checkpoint %s does not match the model configuration" % path)
     file_dtype = torch.bfloat16 if version == 5 else torch.float32
+    if getattr(model, "family", "gpt2") == "llama3":
+        return _load_llama(path, model, file_dtype)
     with open(path, "rb") as f:
         f.seek(1024)
         if file_dtype == model.dtype:
@@ -85,6 +107,80 @@ def load_model(path, model):
                 n = min(CHUNK_ELEMS, flat.numel() - i)
                 _stream_in(f, staging[:n])
                 flat[i:i + n].copy_(staging[:n])
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# LLaMA-3 model files
+
+def _llama_file_tensors(model):
+    """The tensors of a LLaMA model in file order, as lists of flat-buffer views that are contiguous in memory: the fused
+    up-projection (L, 2H, C) is split into its c_fc rows (all layers) followed by its c_fc2 rows (all layers)."""
+    p, L, H = model.params, model.cfg.num_layers, model.cfg.hidden_dim
+    out = []
+    for name in ("wte", "ln1w", "qkvw", "attprojw", "ln2w"):
+        out.append(p[name])
+    out += [p["fc12w"][l, :H] for l in range(L)]
+    out += [p["fc12w"][l, H:] for l in range(L)]
+    for name in ("fcprojw", "lnfw", "lmhead"):
+        out.append(p[name])
+    return out
+
+
+def _write_llama(path, model):
+    cfg = model.cfg
+    header = np.zeros(256, dtype=np.int32)
+    version = 5 if model.dtype == torch.bfloat16 else 3
+    major, minor = (int(x) for x in cfg.version.split("."))
+    header[:16] = [LLAMA_MAGIC, version, cfg.max_seq_len, cfg.vocab_size, cfg.num_layers, cfg.num_heads, cfg.num_kv_heads,
+                   cfg.channels, int(cfg.ffn_dim_multiplier), cfg.multiple_of, int(cfg.norm_eps), int(cfg.rope_theta),
+                   int(cfg.use_scaled_rope), 4, major, minor]
+    header[16] = 1
+    header[17:23] = np.array([cfg.ffn_dim_multiplier, cfg.norm_eps, cfg.rope_theta], dtype=np.float64).view(np.int32)
+    header[23] = cfg.padded_vocab_size
+    Vp, V = cfg.padded_vocab_size, cfg.vocab_size
+    with open(path, "wb") as f:
+        f.write(header.tobytes())
+        for t in _llama_file_tensors(model):
+            if t.shape[0] == Vp and t.dim() == 2 and Vp != V:
+                t = t[:V]                      # files hold the unpadded vocabulary, like the reference's
+            _stream_out(f, t)
+
+
+def _read_llama_header(header, path):
+    from ..models.llama3 import LlamaConfig, _pad128
+    if header[1] not in (3, 5):
+        raise ValueError("unsupported model file version %d (3 = fp32, 5 = bf16)" % header[1])
+    if header[16] == 1:
+        ffn, eps, theta = (float(x) for x in np.ascontiguousarray(header[17:23]).view(np.float64))
+        vp = int(header[23])
+    else:
+        # a file from the reference's writer: the float fields were truncated to integers; LLaMA-3.1 values
+        ffn, eps, theta, vp = (1.2 if header[7] == 16384 else 1.3), 1e-5, float(header[11]), _pad128(int(header[3]))
+    cfg = LlamaConfig(max_seq_len=int(header[2]), vocab_size=int(header[3]), padded_vocab_size=vp, num_layers=int(header[4]),
+                      num_heads=int(header[5]), num_kv_heads=int(header[6]), channels=int(header[7]), ffn_dim_multiplier=ffn,
+                      multiple_of=int(header[9]), norm_eps=eps, rope_theta=theta, use_scaled_rope=bool(header[12]),
+                      version="%d.%d" % (header[14], header[15]))
+    return cfg, int(header[1])
+
+
+def _load_llama(path, model, file_dtype):
+    cfg = model.cfg
+    Vp, V = cfg.padded_vocab_size, cfg.vocab_size
+    staging = None if file_dtype == model.dtype else torch.empty(CHUNK_ELEMS, dtype=file_dtype)
+    with open(path, "rb") as f:
+        f.seek(1024)
+        for t in _llama_file_tensors(model):
+            if t.shape[0] == Vp and t.dim() == 2 and Vp != V:
+                t[V:].zero_()
+                t = t[:V]
+            flat = t.reshape(-1)               # a view: every listed tensor is contiguous in the flat buffer
+            if staging is None:
+                _stream_in(f, flat)
+            else:
+                for i in range(0, flat.numel(), CHUNK_ELEMS):
+                    n = min(CHUNK_ELEMS, flat.numel() - i)
+                    _stream_in(f, staging[:n])
+                    flat[i:i + n].copy_(staging[:n])
 
 
 def write_state(path, *, num_processes, process_rank, use_master_weights, step, rng_state, rng_state_last_update, m, v, master,

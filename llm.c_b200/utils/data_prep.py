@@ -16,23 +16,25 @@ import numpy as np
 from .dataloader import write_datafile, write_evalfile
 
 
-def shard_documents(docs, encode, prefix, eot=50256, shard_size=10 ** 8):
-    """docs: iterable of strings.  Returns the list of files written."""
-    files, buf, count, shard = [], np.empty(shard_size, dtype=np.uint16), 0, 0
+def shard_documents(docs, encode, prefix, eot=50256, shard_size=10 ** 8, model_desc="gpt-2"):
+    """docs: iterable of strings.  Returns the list of files written.  ``model_desc`` "llama-3" writes uint32 shards
+    (pass that tokenizer's end-of-text id, 128000 in the reference, as ``eot``)."""
+    wide = model_desc == "llama-3"
+    files, buf, count, shard = [], np.empty(shard_size, dtype=np.uint32 if wide else np.uint16), 0, 0
 
     def flush(n):
         nonlocal shard
         split = "val" if shard == 0 else "train"
         path = "%s_%s_%06d.bin" % (prefix, split, shard)
-        write_datafile(path, buf[:n])
+        write_datafile(path, buf[:n], model_desc)
         files.append(path)
         shard += 1
 
     for doc in docs:
         toks = np.asarray([eot] + list(encode(doc)), dtype=np.int64)
-        if toks.max(initial=0) >= 2 ** 16:
+        if not wide and toks.max(initial=0) >= 2 ** 16:
             raise ValueError("token id does not fit uint16")
-        toks = toks.astype(np.uint16)
+        toks = toks.astype(buf.dtype)
         while toks.size:
             take = min(shard_size - count, toks.size)
             buf[count:count + take] = toks[:take]
@@ -46,10 +48,10 @@ def shard_documents(docs, encode, prefix, eot=50256, shard_size=10 ** 8):
     return files
 
 
-def write_split(tokens, prefix, val_tokens=32768):
-    tokens = np.asarray(tokens, dtype=np.uint16)
-    write_datafile(prefix + "_val.bin", tokens[:val_tokens])
-    write_datafile(prefix + "_train.bin", tokens[val_tokens:])
+def write_split(tokens, prefix, val_tokens=32768, model_desc="gpt-2"):
+    tokens = np.asarray(tokens, dtype=np.uint32 if model_desc == "llama-3" else np.uint16)
+    write_datafile(prefix + "_val.bin", tokens[:val_tokens], model_desc)
+    write_datafile(prefix + "_train.bin", tokens[val_tokens:], model_desc)
     return prefix + "_train.bin", prefix + "_val.bin"
 
 

@@ -1,7 +1,8 @@
 """Token-shard and evaluation-file loaders over the C++ host runtime, plus the writers of both formats.
 
 Formats (identical to the reference, dev/data/data_common.py and llmc/dataloader.h):
-  token shard  256 x int32 header {20240520, 1, ntok} followed by ntok x uint16
+  token shard  256 x int32 header {20240520, 1, ntok} followed by ntok x uint16, or {20240801, 7, ntok} followed by
+               ntok x uint32 (LLaMA-3 vocabulary)
   eval file    256 x int32 header {20240522, 1, num_examples, longest_example_bytes} followed by, per example, the
                uint16 stream  65535, bytes, index, label, 4, ctx_len, ctx..., (len, tokens...) x 4
 
@@ -18,11 +19,17 @@ from . import _hostlib
 from .rand import STATE_BYTES
 
 
-def write_datafile(path, tokens):
-    """tokens: iterable/array of ints < 65536."""
-    arr = np.asarray(tokens, dtype=np.uint16)
+def write_datafile(path, tokens, model_desc="gpt-2"):
+    """Token shard writer.  ``gpt-2``: ints < 65536 stored as uint16 (magic 20240520, version 1); ``llama-3``: uint32
+    (magic 20240801, version 7), as the reference's dev/data/data_common.py:26-60 writes them."""
+    if model_desc == "llama-3":
+        arr = np.asarray(tokens, dtype=np.uint32)
+        magic, version = 20240801, 7
+    else:
+        arr = np.asarray(tokens, dtype=np.uint16)
+        magic, version = 20240520, 1
     header = np.zeros(256, dtype=np.int32)
-    header[0], header[1], header[2] = 20240520, 1, arr.size
+    header[0], header[1], header[2] = magic, version, arr.size
     with open(path, "wb") as f:
         f.write(header.tobytes())
         f.write(arr.tobytes())
@@ -31,7 +38,10 @@ def write_datafile(path, tokens):
 def write_synthetic_shard(path, ntok, vocab_size=50257, seed=0):
     """Seeded uniform-random uint16 tokens in [0, vocab_size): the synthetic data of the benchmarks."""
     rng = np.random.default_rng(seed)
-    write_datafile(path, rng.integers(0, vocab_size, size=ntok, dtype=np.uint16))
+    if vocab_size > 65536:
+        write_datafile(path, rng.integers(0, vocab_size, size=ntok, dtype=np.uint32), "llama-3")
+    else:
+        write_datafile(path, rng.integers(0, vocab_size, size=ntok, dtype=np.uint16))
 
 
 def write_evalfile(path, examples):

@@ -29,3 +29,38 @@ def oracle_loss_and_grads(model, tokens, targets):
     loss = F.cross_entropy(logits[..., :cfg.vocab_size].reshape(B * T, -1), targets.reshape(-1).long())
     loss.backward()
     return logits.detach(), loss.item(), {k: v.grad for k, v in p.items()}
+
+
+def llama_oracle_loss_and_grads(model, tokens, targets):
+    """The LLaMA-3 forward pass with differentiable PyTorch ops: complex-number rotary embedding, repeat_interleave for the
+    grouped-query heads, silu-gated MLP (the role train_llama3.py plays in the reference)."""
+    cfg = model.cfg
+    p = {k: v.detach().float().cpu().clone().requires_grad_(True) for k, v in model.params.items()}
+    B, T = tokens.shape
+    C, NH, NKV, HS, H = cfg.channels, cfg.num_heads, cfg.num_kv_heads, cfg.head_size, cfg.hidden_dim
+    tab = model.freqs.detach().float().cpu()[:T]
+    rot = torch.complex(tab[..., 0], tab[..., 1]).view(1, T, 1, HS // 2)
+
+    def rms(x, w):
+        return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + cfg.norm_eps) * w
+
+    def rope(t):
+        tc = torch.view_as_complex(t.reshape(*t.shape[:-1], -1, 2).contiguous())
+        return torch.view_as_real(tc * rot).flatten(3)
+
+    x = p["wte"][tokens.long()]
+    for l in range(cfg.num_layers):
+        qkv = rms(x, p["ln1w"][l]) @ p["qkvw"][l].t()
+        q, k, v = qkv.split([NH * HS, NKV * HS, NKV * HS], dim=-1)
+        q, k, v = q.view(B, T, NH, HS), k.view(B, T, NKV, HS), v.view(B, T, NKV, HS)
+        q, k = rope(q), rope(k)
+        k, v = k.repeat_interleave(NH // NKV, dim=2), v.repeat_interleave(NH // NKV, dim=2)
+        q, k, v = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+        y = F.scaled_dot_product_attention(q, k, v, is_causal=True).transpose(1, 2).reshape(B, T, C)
+        x = x + y @ p["attprojw"][l].t()
+        h = rms(x, p["ln2w"][l]) @ p["fc12w"][l].t()
+        x = x + (h[..., :H] * F.silu(h[..., H:])) @ p["fcprojw"][l].t()
+    logits = rms(x, p["lnfw"]) @ p["lmhead"].t()
+    loss = F.cross_entropy(logits[..., :cfg.vocab_size].reshape(B * T, -1), targets.reshape(-1).long())
+    loss.backward()
+    return logits.detach(), loss.item(), {k: v.grad for k, v in p.items()}

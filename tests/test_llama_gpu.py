@@ -1,0 +1,168 @@
+"""LLaMA-3 family on a B200: each new kernel against the PyTorch fp32 restatement of the same operator, then the whole
+bf16 model against the fp32 CPU path of the same model code (logits, loss, every gradient tensor), training and
+bit-exact determinism."""
+import math
+
+import pytest
+import torch
+
+from llmc_b200.models import llama3
+from llmc_b200.ops import kernels as KN
+from llmc_b200.ops import reference as R
+from llmc_b200.parallel.dist import DistConfig
+from llmc_b200.parallel.zero import ShardedAdamW
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def rnd(*shape, scale=1.0, dtype=torch.bfloat16, seed=0):
+    g = torch.Generator().manual_seed(seed + sum(shape))
+    return (torch.randn(*shape, generator=g) * scale).to(dtype)
+
+
+def close(got, want, atol, rtol, what):
+    got, want = got.float().cpu(), want.float().cpu()
+    err = (got - want).abs()
+    bad = (err > atol + rtol * want.abs()).sum().item()
+    assert bad == 0, "%s: %d/%d elements off, max err %.4g (max ref %.4g)" % (what, bad, err.numel(), err.max().item(), want.abs().max().item())
+
+
+@pytest.mark.parametrize("N,C", [(64, 64), (300, 768), (257, 2048), (130, 4096), (40, 8192), (24, 16384)])
+def test_rmsnorm_forward_backward(N, C):
+    x, x2, w, dy = rnd(N, C), rnd(N, C, seed=1), (1.0 + 0.2 * rnd(C, seed=2).float()).to(torch.bfloat16), rnd(N, C, seed=3)
+    out = torch.empty(N, C, dtype=torch.bfloat16, device=DEV)
+    rstd = torch.empty(N, dtype=torch.float32, device=DEV)
+    KN.rmsnorm_forward(out, rstd, x.to(DEV), w.to(DEV), 1e-5)
+    ro, rr = torch.empty(N, C, dtype=torch.bfloat16), torch.empty(N)
+    R.rmsnorm_forward(ro, rr, x, w, 1e-5)
+    close(out, ro, 2e-2, 1e-2, "rmsnorm fwd")
+    close(rstd, rr, 1e-5, 1e-4, "rmsnorm rstd")
+    # fused residual
+    res = torch.empty(N, C, dtype=torch.bfloat16, device=DEV)
+    KN.rmsnorm_fused_residual_forward(res, out, rstd, x.to(DEV), x2.to(DEV), w.to(DEV), 1e-5)
+    rres = torch.empty(N, C, dtype=torch.bfloat16)
+    R.rmsnorm_fused_residual_forward(rres, ro, rr, x, x2, w, 1e-5)
+    assert torch.equal(res.cpu(), rres)
+    close(out, ro, 3e-2, 1e-2, "fused rmsnorm fwd")
+    close(rstd, rr, 1e-5, 1e-4, "fused rmsnorm rstd")
+    # backward, both accumulate settings
+    for acc in (False, True):
+        dx0, dw0 = rnd(N, C, seed=5), rnd(C, seed=6)
+        dx, dw = dx0.to(DEV).clone(), dw0.to(DEV).clone()
+        KN.rmsnorm_backward(dx, dw, dy.to(DEV), rres.to(DEV), w.to(DEV), rstd, accumulate_dinp=acc, accumulate_dw=acc)
+        rdx, rdw = dx0.float().clone(), dw0.float().clone()
+        R.rmsnorm_backward(rdx, rdw, dy, rres, w, rr, accumulate_dinp=acc, accumulate_dw=acc)
+        close(dx, rdx, 3e-2, 2e-2, "rmsnorm dinp acc=%s" % acc)
+        close(dw, rdw, 0.02 * math.sqrt(N) + 0.05, 2e-2, "rmsnorm dweight acc=%s" % acc)
+        dx2, dw2 = dx0.to(DEV).clone(), dw0.to(DEV).clone()
+        KN.rmsnorm_backward(dx2, dw2, dy.to(DEV), rres.to(DEV), w.to(DEV), rstd, accumulate_dinp=acc, accumulate_dw=acc)
+        assert torch.equal(dx, dx2) and torch.equal(dw, dw2)
+
+
+@pytest.mark.parametrize("B,T,NH,NKV,HS", [(2, 64, 4, 2, 64), (1, 128, 8, 8, 64), (3, 32, 8, 2, 128), (2, 16, 6, 1, 96)])
+def test_rope_forward_backward(B, T, NH, NKV, HS):
+    cfg = llama3.LlamaConfig(max_seq_len=2 * T, num_heads=NH, num_kv_heads=NKV, channels=NH * HS)
+    freqs = llama3.rope_table(cfg)
+    N, QR = B * T, (NH + 2 * NKV) * HS
+    raw = rnd(N, QR)
+    packed = torch.full((N, 3 * NH * HS), float("nan"), dtype=torch.bfloat16, device=DEV)
+    KN.rope_forward(packed, raw.to(DEV), freqs.to(DEV), T, NH, NKV)
+    ref = torch.empty(N, 3 * NH * HS, dtype=torch.bfloat16)
+    R.rope_forward(ref, raw, freqs, T, NH, NKV)
+    close(packed, ref, 1e-2, 1e-2, "rope fwd")
+    dpacked = rnd(N, 3 * NH * HS, seed=4)
+    draw = torch.full((N, QR), float("nan"), dtype=torch.bfloat16, device=DEV)
+    KN.rope_backward(draw, dpacked.to(DEV), freqs.to(DEV), T, NH, NKV)
+    rdraw = torch.empty(N, QR)
+    R.rope_backward(rdraw, dpacked, freqs, T, NH, NKV)
+    close(draw, rdraw, 2e-2, 1e-2, "rope bwd")
+
+
+@pytest.mark.parametrize("N,H", [(64, 64), (300, 1032), (129, 14336)])
+def test_swiglu_forward_backward(N, H):
+    x12, dh = rnd(N, 2 * H, scale=2.0), rnd(N, H, seed=3)
+    h = torch.empty(N, H, dtype=torch.bfloat16, device=DEV)
+    KN.swiglu_forward(h, x12.to(DEV))
+    rh = torch.empty(N, H)
+    R.swiglu_forward(rh, x12)
+    close(h, rh, 2e-2, 1e-2, "swiglu fwd")
+    dx = torch.full((N, 2 * H), float("nan"), dtype=torch.bfloat16, device=DEV)
+    KN.swiglu_backward(dx, dh.to(DEV), x12.to(DEV))
+    rdx = torch.empty(N, 2 * H)
+    R.swiglu_backward(rdx, dh, x12)
+    close(dx, rdx, 3e-2, 1e-2, "swiglu bwd")
+
+
+def test_encoder_without_position_table():
+    B, T, C, V = 2, 64, 128, 300
+    g = torch.Generator().manual_seed(0)
+    tok = torch.randint(0, V, (B, T), generator=g, dtype=torch.int32)
+    wte, dout = rnd(V, C), rnd(B, T, C, seed=2)
+    out = torch.empty(B, T, C, dtype=torch.bfloat16, device=DEV)
+    KN.encoder_forward(out, tok.to(DEV), wte.to(DEV), None)
+    assert torch.equal(out.cpu(), wte[tok.long()])
+    dwte = torch.full((V, C), 3.0, dtype=torch.bfloat16, device=DEV)
+    KN.encoder_backward(dwte, None, dout.to(DEV), tok.to(DEV), accumulate_wte=False, accumulate_wpe=False, seed=1)
+    ref = torch.zeros(V, C)
+    R.encoder_backward(ref, None, dout, tok, accumulate_wte=False, accumulate_wpe=False)
+    close(dwte, ref, 5e-2, 2e-2, "encoder bwd without wpe")
+
+
+def make(device, dtype, recompute=0, desc="llama3:l=2,c=256,h=4,kv=2,t=128,v=1000,m=128,f=1.0"):
+    m = llama3.Llama(llama3.config_from_descriptor(desc), device, dtype, recompute=recompute)
+    m.init_random(42)
+    return m
+
+
+def batch(cfg, B, T, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    tok = torch.randint(0, cfg.vocab_size, (B, T + 1), generator=g, dtype=torch.int32)
+    return tok[:, :-1].contiguous(), tok[:, 1:].contiguous()
+
+
+@pytest.mark.parametrize("recompute,desc", [(0, "llama3:l=2,c=256,h=4,kv=2,t=128,v=1000,m=128,f=1.0"),
+                                            (1, "llama3:l=2,c=256,h=2,kv=1,t=128,v=1000,m=64,f=1.3"),
+                                            (2, "llama3:l=2,c=192,h=2,kv=2,t=128,v=1000,m=128,f=1.0")])
+def test_gpu_matches_cpu_reference(recompute, desc):
+    gm = make("cuda", torch.bfloat16, recompute, desc)
+    cm = make("cpu", torch.float32, recompute, desc)
+    cm.params_flat.copy_(gm.params_flat.float().cpu())
+    x, y = batch(gm.cfg, 4, 128)
+    cm.forward(x, y, write_dlogits=False)
+    gm.forward(x.cuda(), y.cuda(), write_dlogits=False)
+    V = gm.cfg.vocab_size
+    lg, lc = gm.logits()[..., :V].float().cpu(), cm.logits()[..., :V]
+    assert (lg - lc).abs().max() < 0.05 + 0.02 * lc.abs().max(), (lg - lc).abs().max()
+    cm.forward(x, y)
+    cm.backward()
+    gm.forward(x.cuda(), y.cuda())
+    gm.backward()
+    assert abs(float(gm.loss()) - float(cm.loss())) < 2e-2
+    for name in llama3.PARAM_NAMES:
+        got, want = gm.grads[name].float().cpu(), cm.grads[name]
+        scale = want.abs().max().item() + 1e-6
+        err = (got - want).abs().max().item()
+        assert err < 0.06 * scale + 1e-4, "gradient of %s: max err %g vs max %g" % (name, err, scale)
+
+
+def test_gpu_training_reduces_loss_and_is_deterministic():
+    runs = []
+    for _ in range(2):
+        m = make("cuda", torch.bfloat16, 0)
+        opt = ShardedAdamW(m, DistConfig(0, 1, 0, torch.device("cuda", 0)), 0, True)
+        x, y = batch(m.cfg, 4, 128)
+        x, y = x.cuda(), y.cuda()
+        losses = []
+        for step in range(8):
+            for micro in range(2):
+                m.forward(x[2 * micro:2 * micro + 2].contiguous(), y[2 * micro:2 * micro + 2].contiguous(), 2, micro)
+                m.backward(micro, micro == 1)
+            losses.append(float(m.loss(2)))
+            opt.grad_norm_sq()
+            opt.step(3e-3, 0.1, step + 1)
+        runs.append((losses, m.params_flat.clone()))
+    l0, p0 = runs[0]
+    l1, p1 = runs[1]
+    assert l0[0] > math.log(1000) - 0.5 and l0[-1] < l0[0] - 0.5, l0
+    assert l0 == l1 and torch.equal(p0, p1), "two identical runs must agree bit for bit"
