@@ -115,9 +115,9 @@ class GPT:
         self.device = torch.device(device)
         if dtype is None:
             dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
-        if self.device.type == "cuda" and dtype != torch.bfloat16:
-            raise ValueError("the sm_100a kernels are bf16; use the CPU path for fp32")
-        if cfg.channels % 8 or (self.device.type == "cuda" and (cfg.head_size % 8 or not 64 <= cfg.head_size <= 128)):
+        if dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError("parameters are bf16 (sm_100a kernels) or fp32 (full-precision mode)")
+        if cfg.channels % 8 or (self.device.type == "cuda" and dtype == torch.bfloat16 and (cfg.head_size % 8 or not 64 <= cfg.head_size <= 128)):
             raise ValueError("channels must be a multiple of 8 and (on the GPU) the head size a multiple of 8 from 64 to 128")
         self.dtype = dtype
         self.recompute = recompute

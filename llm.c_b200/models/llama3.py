@@ -140,10 +140,10 @@ class Llama:
         self.device = torch.device(device)
         if dtype is None:
             dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
-        if self.device.type == "cuda" and dtype != torch.bfloat16:
-            raise ValueError("the sm_100a kernels are bf16; use the CPU path for fp32")
+        if dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError("parameters are bf16 (sm_100a kernels) or fp32 (full-precision mode)")
         hs = cfg.head_size
-        if cfg.channels % 8 or hs % 8 or cfg.hidden_dim % 8 or (self.device.type == "cuda" and not 64 <= hs <= 128):
+        if cfg.channels % 8 or hs % 8 or cfg.hidden_dim % 8 or (self.device.type == "cuda" and dtype == torch.bfloat16 and not 64 <= hs <= 128):
             raise ValueError("channels, head size and MLP width must be multiples of 8 and (on the GPU) the head size within 64..128")
         self.dtype = dtype
         self.recompute = recompute

@@ -6,9 +6,12 @@ buffers) and exists in two implementations with the same signature:
 * ``kernels``    the hand-written sm_100a CUDA kernels (device tensors),
 * ``reference``  a plain PyTorch fp32 restatement (CPU tensors; also the numerics oracle of the tests).
 
-The functions exported here dispatch on the device of their first tensor argument.  A device tensor
-never falls back to PyTorch: if the kernel library is missing the call raises.
+The functions exported here dispatch on the device and type of their first tensor argument: bf16 device tensors go
+to the sm_100a kernels and never fall back to PyTorch (if the kernel library is missing the call raises); fp32
+tensors, on the host or on a device (the legacy full-precision mode), go to the restatement.
 """
+import torch
+
 from . import kernels, reference
 
 _NAMES = [
@@ -21,11 +24,17 @@ _NAMES = [
 ]
 
 
+# operators whose first argument is an fp32 statistic or master copy in every mode: the second argument decides
+_DECIDED_BY_SECOND = {"global_norm_sq", "master_from_params"}
+
+
 def _dispatch(name):
     k, r = getattr(kernels, name), getattr(reference, name)
+    which = 1 if name in _DECIDED_BY_SECOND else 0
 
-    def op(first, *args, **kwargs):
-        return (k if first.is_cuda else r)(first, *args, **kwargs)
+    def op(*args, **kwargs):
+        t = args[which]
+        return (k if (t.is_cuda and t.dtype != torch.float32) else r)(*args, **kwargs)
 
     op.__name__ = name
     op.__doc__ = k.__doc__

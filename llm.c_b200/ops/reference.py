@@ -1,8 +1,10 @@
 """Plain PyTorch restatement of every operator (fp32 math, any storage dtype).
 
 It is the CPU execution path of the framework (fp32 training on the host, the counterpart of the
-reference's train_gpt2.c) and the numerics oracle the kernel tests compare against.  Signatures
-match ``kernels`` exactly: outputs are written in place.
+reference's train_gpt2.c), the numerics oracle the kernel tests compare against, and the fp32 mode on a GPU
+(``-dt fp32`` on a CUDA device, the counterpart of the reference's legacy train_gpt2_fp32.cu: every tensor fp32, the
+operators executed by PyTorch's own CUDA library on the tensors' device).  Signatures match ``kernels`` exactly:
+outputs are written in place.
 """
 import math
 
@@ -72,7 +74,7 @@ def encoder_backward(dwte, dwpe, dout, tokens, accumulate_wte=True, accumulate_w
         if accumulate_wpe:
             gp = gp + _f(dwpe[:T])
         dwpe[:T].copy_(gp)
-    gw = torch.zeros(dwte.shape, dtype=torch.float32)
+    gw = torch.zeros(dwte.shape, dtype=torch.float32, device=dwte.device)
     gw.index_add_(0, tokens.reshape(-1).long(), d.reshape(B * T, C))
     if accumulate_wte:
         gw = gw + _f(dwte)
@@ -131,7 +133,7 @@ def _split_qkv(qkv, B, T, NH):
 def attention_forward(out, lse, qkv, B, T, NH):
     q, k, v, hs = _split_qkv(qkv, B, T, NH)
     att = (q @ k.transpose(-1, -2)) / math.sqrt(hs)
-    mask = torch.ones(T, T, dtype=torch.bool).tril()
+    mask = torch.ones(T, T, dtype=torch.bool, device=qkv.device).tril()
     att = att.masked_fill(~mask, float("-inf"))
     lse.copy_(torch.logsumexp(att, -1).view_as(lse))
     y = torch.softmax(att, -1) @ v
@@ -142,7 +144,7 @@ def attention_backward(dqkv, dout, qkv, out, lse, B, T, NH):
     q, k, v, hs = _split_qkv(qkv, B, T, NH)
     scale = 1.0 / math.sqrt(hs)
     att = (q @ k.transpose(-1, -2)) * scale
-    mask = torch.ones(T, T, dtype=torch.bool).tril()
+    mask = torch.ones(T, T, dtype=torch.bool, device=qkv.device).tril()
     p = torch.exp(att - _f(lse).view(B, NH, T, 1)).masked_fill(~mask, 0.0)
     do = _f(dout).view(B, T, NH, hs).transpose(1, 2)
     o = _f(out).view(B, T, NH, hs).transpose(1, 2)
@@ -166,8 +168,8 @@ def fused_classifier(logits, losses, targets, dloss, V, write_dlogits=True, accu
     losses.copy_(loss)
     if write_dlogits:
         g = torch.exp(lp)
-        g.scatter_add_(1, targets.long().view(-1, 1), -torch.ones(N, 1))
-        full = torch.zeros(N, Vp)
+        g.scatter_add_(1, targets.long().view(-1, 1), -torch.ones(N, 1, device=logits.device))
+        full = torch.zeros(N, Vp, device=logits.device)
         full[:, :V] = g * dloss
         logits.copy_(full)
 
@@ -190,7 +192,7 @@ def _view_slices(v):
 
 
 def global_norm_sq(out, grads, views):
-    acc = torch.zeros((), dtype=torch.float32)
+    acc = torch.zeros((), dtype=torch.float32, device=grads.device)
     for v in views:
         for pb, _, n in _view_slices(v):
             acc = acc + (_f(grads[pb:pb + n]) ** 2).sum()

@@ -172,7 +172,7 @@ class Trainer:
             load = checkpoint.checkpoint_paths(c.output_log_dir, self.resume_step, d.process_rank)[0]
         # multi-GPU ZeRO-1 on this library's own NVLink kernels: the flat buffers live in symmetric memory
         arena, sym_bufs, allocator = None, {}, None
-        if d.num_processes > 1 and self.device.type == "cuda" and (c.comm_backend or "p2p") == "p2p":
+        if d.num_processes > 1 and self.device.type == "cuda" and dtype != torch.float32 and (c.comm_backend or "p2p") == "p2p":
             from .parallel import p2p
             arena = p2p.try_create(None, d, c.zero_stage, self.print0)
             if arena is not None:
@@ -195,6 +195,10 @@ class Trainer:
         if T > m.cfg.max_seq_len:
             raise ValueError("sequence length %d exceeds the model's maximum %d" % (T, m.cfg.max_seq_len))
         self.precision = "bf16" if m.dtype == torch.bfloat16 else "fp32"
+        if self.device.type == "cuda" and m.dtype == torch.float32:
+            # full-precision mode: -f 1 lets the library GEMMs use TF32 tensor cores, -f 0 keeps them in IEEE fp32
+            # (the same switch as the reference's train_gpt2_fp32.cu / PRECISION=FP32 builds)
+            torch.backends.cuda.matmul.allow_tf32 = bool(c.override_enable_tf32)
 
         # ---- data
         permute = 0 if c.overfit_single_batch == 1 else 1

@@ -86,3 +86,23 @@ def test_gpu_matches_cpu_reference_wide_heads(C, NH):
         got, want = gm.grads[name].float().cpu(), cm.grads[name]
         scale = want.abs().max().item() + 1e-6
         assert (got - want).abs().max().item() < 0.06 * scale + 1e-4, name
+
+
+def test_fp32_mode_on_the_gpu_matches_the_cpu_path():
+    """The legacy full-precision mode (all tensors fp32 on the device) follows the CPU path to fp32 round-off."""
+    torch.backends.cuda.matmul.allow_tf32 = False
+    gm = make("cuda", torch.float32, 1)
+    cm = make("cpu", torch.float32, 1)
+    assert torch.equal(gm.params_flat.cpu(), cm.params_flat)
+    x, y = batch(gm.cfg, 2, 64)
+    for m, dev in ((gm, "cuda"), (cm, "cpu")):
+        m.forward(x.to(dev), y.to(dev))
+        m.backward()
+    assert abs(float(gm.loss()) - float(cm.loss())) < 1e-4
+    assert torch.allclose(gm.grads_flat.cpu(), cm.grads_flat, atol=1e-4, rtol=1e-3)
+    opt = ShardedAdamW(gm, DistConfig(0, 1, 0, torch.device("cuda", 0)), 0, True)
+    assert opt.master is None
+    before = gm.params_flat.clone()
+    opt.grad_norm_sq()
+    opt.step(1e-3, 0.1, 1)
+    assert not torch.equal(before, gm.params_flat) and torch.isfinite(gm.params_flat).all()
