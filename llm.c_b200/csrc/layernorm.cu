@@ -2,10 +2,10 @@
 // activations with fp32 statistics.
 //
 // Forward: one warp per row, 128-bit loads; the second and third pass over the row hit L1.
-// Backward: each CTA walks a contiguous strip of rows; every lane keeps the dweight/dbias partial
-// sums of "its" channels in registers across the strip, the CTA folds its warps in a fixed order
-// and writes one fp32 partial row per CTA; a second tiny kernel folds the CTA partials in CTA order
-// and accumulates into the bf16 gradients.  No float atomics anywhere: results are bit-reproducible.
+// Backward: each CTA walks a contiguous strip of rows with one thread per 8-channel pack, so every thread keeps the
+// dweight/dbias partial sums of "its" channels in registers across the strip and writes one fp32 partial row per CTA;
+// a second tiny kernel folds the CTA partials in a fixed order and accumulates into the bf16 gradients.
+// No float atomics anywhere: results are bit-reproducible.
 //
 // Capability parity: llmc/layernorm.cuh (layernorm_forward, fused_residual_forward5,
 // layernorm_backward) of the reference.
@@ -13,10 +13,8 @@
 
 namespace {
 
-// Backward: MAXP packs (of 8 channels) per lane are held in registers => 32*8*MAXP channels per "slab"
-// (MAXP = 3 covers C <= 768 with fewer registers, MAXP = 4 everything else; rows wider than a slab go slab by slab).
-constexpr int LNB_WARPS = 4;         // warps per CTA of the backward kernel
-constexpr int LNB_CTAS_PER_SM = 4;
+constexpr int LNB_MAX_THREADS = 256;  // threads of a backward CTA: one per 8-channel pack of a row, up to this many
+constexpr int LNB_MAX_CTAS_PER_SM = 16;
 
 template <bool FUSED_RESIDUAL>
 __global__ void __launch_bounds__(256)
@@ -76,229 +74,164 @@ ln_fwd_kernel(bf16* __restrict__ out, float* __restrict__ mean_out, float* __res
     }
 }
 
-// dinp (+)= LN'(dout); per-CTA fp32 partials of dweight/dbias -> partials[cta][2][C].
-// Fast path for rows that fit one warp's registers (C <= 256 * MAXP): the next row's dout / inp / dinp packs are requested
-// before the current row is reduced (two rows of loads in flight per warp); the dweight / dbias partial sums of a warp
-// live in its own slab of shared memory (conflict-free float4 layout), which keeps the register count low enough for
-// four CTAs per SM.
-template <bool ACCUM_DINP, int MAXP, bool COLSUM>
-__global__ void __launch_bounds__(LNB_WARPS * 32, LNB_CTAS_PER_SM)
-ln_bwd_fast_kernel(bf16* __restrict__ dinp, float* __restrict__ partials, const bf16* __restrict__ dout,
-                   const bf16* __restrict__ inp, const bf16* __restrict__ weight,
-                   const float* __restrict__ mean, const float* __restrict__ rstd, int N, int C, int rows_per_cta) {
-    constexpr int NARR = COLSUM ? 3 : 2;
-    extern __shared__ float4 sh4[];     // [warp][NARR (dw, db, column sums of dinp)][MAXP][2 halves][32 lanes]
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+// Backward.  A CTA owns a strip of rows; thread t owns the 8-channel packs t, t + blockDim, ... (MAXP of them) of EVERY
+// row, so
+//   * the weights of its channels are converted to fp32 once,
+//   * its dweight / dbias (/ column-sum) partial sums stay in registers for the whole strip,
+//   * every row element is loaded exactly once, 128 bits at a time.
+// The two row statistics need the whole row: one combined shuffle tree for both values, one shared-memory exchange and
+// ONE barrier per row (the exchange buffer is double buffered by row parity).  With CACHE the fp32 values of the first
+// pass (dout, dout * w, xhat) stay in registers for the second pass, which is then 2 FMAs per element for dinp plus the
+// accumulations.  Per-CTA partial sums go to partials[cta][3][C]; a second kernel folds them in a fixed order.
+// No float atomics: results are bit-reproducible.
+DEVINL float bf16lo(uint32_t u) { return __uint_as_float(u << 16); }
+DEVINL float bf16hi(uint32_t u) { return __uint_as_float(u & 0xffff0000u); }
+
+template <bool ACCUM_DINP, int MAXP, bool COLSUM, bool CACHE>
+__global__ void __launch_bounds__(LNB_MAX_THREADS)
+ln_bwd_col_kernel(bf16* __restrict__ dinp, float* __restrict__ partials, const bf16* __restrict__ dout,
+                  const bf16* __restrict__ inp, const bf16* __restrict__ weight,
+                  const float* __restrict__ mean, const float* __restrict__ rstd, int N, int C, int rows_per_cta) {
+    __shared__ float2 red[2][LNB_MAX_THREADS / 32];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5, nthr = blockDim.x;
+    const int npack = C >> 3;
     const int row0 = blockIdx.x * rows_per_cta;
     const int row1 = min(N, row0 + rows_per_cta);
-    const int npack = C >> 3;
-    float4* wacc = sh4 + (size_t)warp * (NARR * MAXP * 2 * 32);
+    const float inv_c = 1.0f / C;
+    float wf[MAXP][8], dw[MAXP][8], db[MAXP][8], dc[COLSUM ? MAXP : 1][8];
     #pragma unroll
-    for (int k = 0; k < NARR * MAXP * 2; k++) wacc[k * 32 + lane] = make_float4(0.f, 0.f, 0.f, 0.f);
-
-    bf16x8 cd[MAXP], cx[MAXP], co[MAXP];
-    float cm = 0.f, crs = 0.f;
-    auto fetch = [&](int r, bf16x8* d, bf16x8* a, bf16x8* o, float& m_, float& rs_) {
-        const bf16* dy = dout + (size_t)r * C;
-        const bf16* x = inp + (size_t)r * C;
-        const bf16* dx = dinp + (size_t)r * C;
+    for (int i = 0; i < MAXP; i++) {
+        const int p = tid + nthr * i;
+        uint4 w = make_uint4(0u, 0u, 0u, 0u);
+        if (p < npack) w = *reinterpret_cast<const uint4*>(weight + p * 8);
+        const uint32_t wu[4] = {w.x, w.y, w.z, w.w};
+        #pragma unroll
+        for (int k = 0; k < 4; k++) { wf[i][2 * k] = bf16lo(wu[k]); wf[i][2 * k + 1] = bf16hi(wu[k]); }
+        #pragma unroll
+        for (int e = 0; e < 8; e++) { dw[i][e] = 0.f; db[i][e] = 0.f; if (COLSUM) dc[i][e] = 0.f; }
+    }
+    for (int row = row0; row < row1; row++) {
+        const size_t rbase = (size_t)row * C;
+        uint4 dq[MAXP], xq[MAXP], oq[MAXP];
         #pragma unroll
         for (int i = 0; i < MAXP; i++) {
-            const int p = lane + 32 * i;
+            const int p = tid + nthr * i;
+            dq[i] = make_uint4(0u, 0u, 0u, 0u); xq[i] = dq[i]; oq[i] = dq[i];
             if (p < npack) {
-                d[i] = ld128cs(dy + p * 8); a[i] = ld128cs(x + p * 8);
-                if (ACCUM_DINP) o[i] = ld128cs(dx + p * 8);
+                dq[i] = __ldcs(reinterpret_cast<const uint4*>(dout + rbase + p * 8));
+                xq[i] = __ldcs(reinterpret_cast<const uint4*>(inp + rbase + p * 8));
+                if (ACCUM_DINP) oq[i] = __ldcs(reinterpret_cast<const uint4*>(dinp + rbase + p * 8));
             }
         }
-        m_ = mean[r]; rs_ = rstd[r];
-    };
-    int row = row0 + warp;
-    if (row < row1) fetch(row, cd, cx, co, cm, crs);
-    for (; row < row1; row += nwarps) {
-        bf16x8 nd[MAXP], nx[MAXP], no[MAXP];
-        float nm = 0.f, nrs = 0.f;
-        const int nrow = row + nwarps;
-        if (nrow < row1) fetch(nrow, nd, nx, no, nm, nrs);
-        const float m = cm, rs = crs;
+        const float rs = rstd[row];
+        const float mrs = -mean[row] * rs;                         // xhat = x * rs + mrs
+        float dy[CACHE ? MAXP : 1][8], dn[CACHE ? MAXP : 1][8], nn[CACHE ? MAXP : 1][8];
         float s1 = 0.f, s2 = 0.f;
         #pragma unroll
         for (int i = 0; i < MAXP; i++) {
-            const int p = lane + 32 * i;
-            if (p < npack) {
-                bf16x8 w = ld128(weight + p * 8);
-                #pragma unroll
-                for (int e = 0; e < 8; e++) {
-                    float dn = __bfloat162float(cd[i][e]) * __bfloat162float(w[e]);
-                    float nn = (__bfloat162float(cx[i][e]) - m) * rs;
-                    s1 += dn; s2 += dn * nn;
-                }
-            }
-        }
-        s1 = warp_sum(s1) / C; s2 = warp_sum(s2) / C;
-        bf16* dx = dinp + (size_t)row * C;
-        #pragma unroll
-        for (int i = 0; i < MAXP; i++) {
-            const int p = lane + 32 * i;
-            if (p < npack) {
-                bf16x8 w = ld128(weight + p * 8);
-                bf16x8 o;
-                float gw[8], gb[8], gc[8];
-                #pragma unroll
-                for (int e = 0; e < 8; e++) {
-                    float dyv = __bfloat162float(cd[i][e]);
-                    float nn = (__bfloat162float(cx[i][e]) - m) * rs;
-                    float dn = dyv * __bfloat162float(w[e]);
-                    gb[e] = dyv;
-                    gw[e] = dyv * nn;
-                    float v = (dn - s1 - nn * s2) * rs;
-                    if (ACCUM_DINP) v += __bfloat162float(co[i][e]);
-                    o[e] = __float2bfloat16_rn(v);
-                    gc[e] = __bfloat162float(o[e]);      // what the consumer of dinp will read
-                }
-                st128(dx + p * 8, o);
-                #pragma unroll
-                for (int hf = 0; hf < 2; hf++) {
-                    float4* aw = &wacc[((0 * MAXP + i) * 2 + hf) * 32 + lane];
-                    float4* ab = &wacc[((1 * MAXP + i) * 2 + hf) * 32 + lane];
-                    float4 tw = *aw, tb = *ab;
-                    tw.x += gw[hf * 4 + 0]; tw.y += gw[hf * 4 + 1]; tw.z += gw[hf * 4 + 2]; tw.w += gw[hf * 4 + 3];
-                    tb.x += gb[hf * 4 + 0]; tb.y += gb[hf * 4 + 1]; tb.z += gb[hf * 4 + 2]; tb.w += gb[hf * 4 + 3];
-                    *aw = tw; *ab = tb;
-                    if (COLSUM) {
-                        float4* ac = &wacc[((2 * MAXP + i) * 2 + hf) * 32 + lane];
-                        float4 tc = *ac;
-                        tc.x += gc[hf * 4 + 0]; tc.y += gc[hf * 4 + 1]; tc.z += gc[hf * 4 + 2]; tc.w += gc[hf * 4 + 3];
-                        *ac = tc;
-                    }
-                }
-            }
-        }
-        #pragma unroll
-        for (int i = 0; i < MAXP; i++) { cd[i] = nd[i]; cx[i] = nx[i]; co[i] = no[i]; }
-        cm = nm; crs = nrs;
-    }
-    // fold the warps of this CTA in warp order
-    __syncthreads();
-    float* part = partials + (size_t)blockIdx.x * 3 * C;
-    const float* shf = reinterpret_cast<const float*>(sh4);
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
-        const int p = c >> 3, e = c & 7;
-        const int i = p >> 5, ln = p & 31, hf = e >> 2, comp = e & 3;
-        float a = 0.f, b = 0.f, cs = 0.f;
-        for (int w = 0; w < nwarps; w++) {
-            const size_t base = (size_t)w * (NARR * MAXP * 2 * 32) * 4;
-            a += shf[base + ((((0 * MAXP + i) * 2 + hf) * 32 + ln) * 4) + comp];
-            b += shf[base + ((((1 * MAXP + i) * 2 + hf) * 32 + ln) * 4) + comp];
-            if (COLSUM) cs += shf[base + ((((2 * MAXP + i) * 2 + hf) * 32 + ln) * 4) + comp];
-        }
-        part[c] = a;
-        part[C + c] = b;
-        if (COLSUM) part[2 * C + c] = cs;
-    }
-}
-
-// Generic path (rows wider than one warp's registers): channel slabs of 1024, partial sums in registers.
-template <bool ACCUM_DINP>
-__global__ void __launch_bounds__(LNB_WARPS * 32)
-ln_bwd_kernel(bf16* __restrict__ dinp, float* __restrict__ partials, const bf16* __restrict__ dout,
-              const bf16* __restrict__ inp, const bf16* __restrict__ weight,
-              const float* __restrict__ mean, const float* __restrict__ rstd, int N, int C, int rows_per_cta) {
-    constexpr int MAXP = 4;
-    extern __shared__ float sh[];   // [warps][2][slab] only during the fold
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-    const int row0 = blockIdx.x * rows_per_cta;
-    const int row1 = min(N, row0 + rows_per_cta);
-    const int npack = C >> 3;
-    const int slab_packs = 32 * MAXP;
-    float* part = partials + (size_t)blockIdx.x * 3 * C;
-
-    for (int slab0 = 0; slab0 < npack; slab0 += slab_packs) {
-        float dw[MAXP][8], db[MAXP][8];
-        #pragma unroll
-        for (int i = 0; i < MAXP; i++)
-            #pragma unroll
-            for (int e = 0; e < 8; e++) { dw[i][e] = 0.f; db[i][e] = 0.f; }
-        for (int row = row0 + warp; row < row1; row += nwarps) {
-            const bf16* dy = dout + (size_t)row * C;
-            const bf16* x = inp + (size_t)row * C;
-            const float m = mean[row], rs = rstd[row];
-            float s1 = 0.f, s2 = 0.f;           // row-wide sums (needed for every slab)
-            for (int p = lane; p < npack; p += 32) {
-                bf16x8 d = ld128(dy + p * 8), a = ld128(x + p * 8), w = ld128(weight + p * 8);
-                #pragma unroll
-                for (int e = 0; e < 8; e++) {
-                    float dn = __bfloat162float(d[e]) * __bfloat162float(w[e]);
-                    float nn = (__bfloat162float(a[e]) - m) * rs;
-                    s1 += dn; s2 += dn * nn;
-                }
-            }
-            s1 = warp_sum(s1) / C; s2 = warp_sum(s2) / C;
-            bf16* dx = dinp + (size_t)row * C;
-            #pragma unroll
-            for (int i = 0; i < MAXP; i++) {
-                const int p = slab0 + lane + 32 * i;
-                if (p < npack) {
-                    bf16x8 d = ld128(dy + p * 8), a = ld128(x + p * 8), w = ld128(weight + p * 8);
-                    bf16x8 o;
-                    if (ACCUM_DINP) o = ld128(dx + p * 8);
-                    #pragma unroll
-                    for (int e = 0; e < 8; e++) {
-                        float dyv = __bfloat162float(d[e]);
-                        float nn = (__bfloat162float(a[e]) - m) * rs;
-                        float dn = dyv * __bfloat162float(w[e]);
-                        db[i][e] += dyv;
-                        dw[i][e] += dyv * nn;
-                        float v = (dn - s1 - nn * s2) * rs;
-                        if (ACCUM_DINP) v += __bfloat162float(o[e]);
-                        o[e] = __float2bfloat16_rn(v);
-                    }
-                    st128(dx + p * 8, o);
-                }
-            }
-        }
-        // fold the warps of this CTA in warp order
-        const int slab_ch = slab_packs * 8;
-        __syncthreads();
-        #pragma unroll
-        for (int i = 0; i < MAXP; i++) {
-            const int lc = (lane + 32 * i) * 8;
+            const uint32_t du[4] = {dq[i].x, dq[i].y, dq[i].z, dq[i].w}, xu[4] = {xq[i].x, xq[i].y, xq[i].z, xq[i].w};
             #pragma unroll
             for (int e = 0; e < 8; e++) {
-                sh[(warp * 2 + 0) * slab_ch + lc + e] = dw[i][e];
-                sh[(warp * 2 + 1) * slab_ch + lc + e] = db[i][e];
+                const float d_ = (e & 1) ? bf16hi(du[e >> 1]) : bf16lo(du[e >> 1]);
+                const float x_ = (e & 1) ? bf16hi(xu[e >> 1]) : bf16lo(xu[e >> 1]);
+                const float dn_ = d_ * wf[i][e];
+                const float nn_ = fmaf(x_, rs, mrs);
+                s1 += dn_; s2 = fmaf(dn_, nn_, s2);
+                if (CACHE) { dy[i][e] = d_; dn[i][e] = dn_; nn[i][e] = nn_; }
             }
         }
-        __syncthreads();
-        for (int c = threadIdx.x; c < slab_ch; c += blockDim.x) {
-            const int gc = slab0 * 8 + c;
-            if (gc < C) {
-                float a = 0.f, b = 0.f;
-                for (int w = 0; w < nwarps; w++) { a += sh[(w * 2 + 0) * slab_ch + c]; b += sh[(w * 2 + 1) * slab_ch + c]; }
-                part[gc] = a;
-                part[C + gc] = b;
-            }
+        // both sums through one shuffle tree: after the first exchange even lanes carry s1, odd lanes s2
+        {
+            const bool odd = lane & 1;
+            float keep = odd ? s2 : s1;
+            const float send = odd ? s1 : s2;
+            keep += __shfl_xor_sync(0xffffffffu, send, 1);
+            #pragma unroll
+            for (int o_ = 2; o_ < 32; o_ <<= 1) keep += __shfl_xor_sync(0xffffffffu, keep, o_);
+            float* rb = reinterpret_cast<float*>(&red[row & 1][warp]);
+            if (lane < 2) rb[lane] = keep;
         }
         __syncthreads();
+        float t1 = 0.f, t2 = 0.f;
+        for (int w = 0; w < nwarps; w++) { const float2 v = red[row & 1][w]; t1 += v.x; t2 += v.y; }
+        // dinp = rs * (dn - mean(dn) - xhat * mean(dn * xhat)) = dn * rs + (xhat * c2 + c1)
+        const float c1 = -t1 * inv_c * rs, c2 = -t2 * inv_c * rs;
+        #pragma unroll
+        for (int i = 0; i < MAXP; i++) {
+            const int p = tid + nthr * i;
+            const uint32_t du[4] = {dq[i].x, dq[i].y, dq[i].z, dq[i].w}, xu[4] = {xq[i].x, xq[i].y, xq[i].z, xq[i].w};
+            const uint32_t ou[4] = {oq[i].x, oq[i].y, oq[i].z, oq[i].w};
+            uint32_t res[4];
+            #pragma unroll
+            for (int k = 0; k < 4; k++) {
+                float v[2];
+                #pragma unroll
+                for (int hh = 0; hh < 2; hh++) {
+                    const int e = 2 * k + hh;
+                    float d_, dn_, nn_;
+                    if (CACHE) { d_ = dy[i][e]; dn_ = dn[i][e]; nn_ = nn[i][e]; }
+                    else {
+                        d_ = hh ? bf16hi(du[k]) : bf16lo(du[k]);
+                        const float x_ = hh ? bf16hi(xu[k]) : bf16lo(xu[k]);
+                        dn_ = d_ * wf[i][e];
+                        nn_ = fmaf(x_, rs, mrs);
+                    }
+                    db[i][e] += d_;
+                    dw[i][e] = fmaf(d_, nn_, dw[i][e]);
+                    float r_ = fmaf(dn_, rs, fmaf(nn_, c2, c1));
+                    if (ACCUM_DINP) r_ += hh ? bf16hi(ou[k]) : bf16lo(ou[k]);
+                    v[hh] = r_;
+                }
+                res[k] = pack_bf16x2(v[0], v[1]);
+                if (COLSUM) { dc[i][2 * k] += bf16lo(res[k]); dc[i][2 * k + 1] += bf16hi(res[k]); }   // what the consumer of dinp reads
+            }
+            if (p < npack) *reinterpret_cast<uint4*>(dinp + rbase + p * 8) = make_uint4(res[0], res[1], res[2], res[3]);
+        }
+    }
+    float* part = partials + (size_t)blockIdx.x * 3 * C;
+    #pragma unroll
+    for (int i = 0; i < MAXP; i++) {
+        const int p = tid + nthr * i;
+        if (p < npack) {
+            #pragma unroll
+            for (int e = 0; e < 8; e += 4) {
+                *reinterpret_cast<float4*>(part + p * 8 + e) = make_float4(dw[i][e], dw[i][e + 1], dw[i][e + 2], dw[i][e + 3]);
+                *reinterpret_cast<float4*>(part + C + p * 8 + e) = make_float4(db[i][e], db[i][e + 1], db[i][e + 2], db[i][e + 3]);
+                if (COLSUM) *reinterpret_cast<float4*>(part + 2 * C + p * 8 + e) = make_float4(dc[i][e], dc[i][e + 1], dc[i][e + 2], dc[i][e + 3]);
+            }
+        }
     }
 }
 
-// dweight[c] (+)= sum over CTAs (in CTA order) of partials; same for dbias and (optionally) the column sums of dinp
-__global__ void ln_bwd_fold_kernel(bf16* __restrict__ dweight, bf16* __restrict__ dbias, bf16* __restrict__ dcolsum,
-                                   const float* __restrict__ partials, int num_ctas, int C, int accumulate, int accumulate_col) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= C) return;
+// dweight[c] (+)= sum over CTAs of partials, likewise dbias and (optionally) the column sums of dinp.  A block covers 32
+// channels with 8 slices of CTAs; slice y adds CTAs y, y + 8, ... in order and the slices are added in order: a fixed tree.
+__global__ void __launch_bounds__(256)
+ln_bwd_fold_kernel(bf16* __restrict__ dweight, bf16* __restrict__ dbias, bf16* __restrict__ dcolsum,
+                   const float* __restrict__ partials, int num_ctas, int C, int accumulate, int accumulate_col) {
+    __shared__ float sh[3][8][32];
+    const int x = threadIdx.x & 31, y = threadIdx.x >> 5;
+    const int c = blockIdx.x * 32 + x;
     float a = 0.f, b = 0.f, cs = 0.f;
-    for (int i = 0; i < num_ctas; i++) {
-        a += partials[(size_t)i * 3 * C + c];
-        b += partials[(size_t)i * 3 * C + C + c];
-        if (dcolsum) cs += partials[(size_t)i * 3 * C + 2 * C + c];
+    if (c < C) {
+        for (int i = y; i < num_ctas; i += 8) {
+            a += partials[(size_t)i * 3 * C + c];
+            b += partials[(size_t)i * 3 * C + C + c];
+            if (dcolsum) cs += partials[(size_t)i * 3 * C + 2 * C + c];
+        }
     }
-    if (accumulate) { a += __bfloat162float(dweight[c]); b += __bfloat162float(dbias[c]); }
-    dweight[c] = __float2bfloat16_rn(a);
-    dbias[c] = __float2bfloat16_rn(b);
-    if (dcolsum) {
-        if (accumulate_col) cs += __bfloat162float(dcolsum[c]);
-        dcolsum[c] = __float2bfloat16_rn(cs);
+    sh[0][y][x] = a; sh[1][y][x] = b; sh[2][y][x] = cs;
+    __syncthreads();
+    if (y == 0 && c < C) {
+        a = 0.f; b = 0.f; cs = 0.f;
+        #pragma unroll
+        for (int k = 0; k < 8; k++) { a += sh[0][k][x]; b += sh[1][k][x]; cs += sh[2][k][x]; }
+        if (accumulate) { a += __bfloat162float(dweight[c]); b += __bfloat162float(dbias[c]); }
+        dweight[c] = __float2bfloat16_rn(a);
+        dbias[c] = __float2bfloat16_rn(b);
+        if (dcolsum) {
+            if (accumulate_col) cs += __bfloat162float(dcolsum[c]);
+            dcolsum[c] = __float2bfloat16_rn(cs);
+        }
     }
 }
 
@@ -324,50 +257,60 @@ extern "C" int llmc_fused_residual_fwd(bf16* residual, bf16* normed, float* mean
 // Number of fp32 scratch elements llmc_layernorm_bwd needs
 extern "C" long long llmc_layernorm_bwd_scratch(int N, int C) {
     int sms = llmc_device_sm_count(); if (sms <= 0) sms = 148;
-    return (long long)(LNB_CTAS_PER_SM * sms) * 3 * C;
+    return (long long)(LNB_MAX_CTAS_PER_SM * sms) * 3 * C;
 }
 
+namespace {
+struct LnbLaunch { int threads, ctas, rows_per_cta; };
+
+template <bool ACC, int MAXP, bool COL>
+int lnb_launch(bf16* dinp, float* scratch, const bf16* dout, const bf16* inp, const bf16* weight, const float* mean, const float* rstd,
+               int N, int C, int threads, int* ctas_out, cudaStream_t stream) {
+    static int occ_cache[LNB_MAX_THREADS / 32 + 1] = {0};
+    int& occ = occ_cache[threads / 32];
+    if (occ == 0) {
+        CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, ln_bwd_col_kernel<ACC, MAXP, COL, (MAXP <= 2)>, threads, 0));
+        if (occ < 1) occ = 1;
+        if (occ > LNB_MAX_CTAS_PER_SM) occ = LNB_MAX_CTAS_PER_SM;
+    }
+    int sms = llmc_device_sm_count(); if (sms <= 0) sms = 148;
+    int ctas = occ * sms;
+    int rows_per_cta = CEIL_DIV(N, ctas);
+    ctas = CEIL_DIV(N, rows_per_cta);
+    ln_bwd_col_kernel<ACC, MAXP, COL, (MAXP <= 2)><<<ctas, threads, 0, stream>>>(dinp, scratch, dout, inp, weight, mean, rstd, N, C, rows_per_cta);
+    CUDA_CHECK(cudaGetLastError());
+    *ctas_out = ctas;
+    return 0;
+}
+
+template <int MAXP>
+int lnb_dispatch(bool acc, bool col, bf16* dinp, float* scratch, const bf16* dout, const bf16* inp, const bf16* weight,
+                 const float* mean, const float* rstd, int N, int C, int threads, int* ctas_out, cudaStream_t stream) {
+    if (acc) return col ? lnb_launch<true, MAXP, true>(dinp, scratch, dout, inp, weight, mean, rstd, N, C, threads, ctas_out, stream)
+                        : lnb_launch<true, MAXP, false>(dinp, scratch, dout, inp, weight, mean, rstd, N, C, threads, ctas_out, stream);
+    return col ? lnb_launch<false, MAXP, true>(dinp, scratch, dout, inp, weight, mean, rstd, N, C, threads, ctas_out, stream)
+               : lnb_launch<false, MAXP, false>(dinp, scratch, dout, inp, weight, mean, rstd, N, C, threads, ctas_out, stream);
+}
+}  // namespace
+
 // dinp (+)= dLN ; dweight, dbias (+)= column sums.  `scratch` holds llmc_layernorm_bwd_scratch floats.
-// If dcolsum is given (C <= 1024 only) it receives (+)= the column sums of the final dinp: when dinp is the residual-stream
-// gradient, that is the bias gradient of the projection that wrote into the residual stream, obtained without another pass.
+// If dcolsum is given it receives (+)= the column sums of the final dinp: when dinp is the residual-stream gradient, that
+// is the bias gradient of the projection that wrote into the residual stream, obtained without another pass.  C <= 16384.
 extern "C" int llmc_layernorm_bwd(bf16* dinp, bf16* dweight, bf16* dbias, float* scratch, const bf16* dout, const bf16* inp,
                                   const bf16* weight, const float* mean, const float* rstd, int N, int C,
                                   int accumulate_dinp, int accumulate_dwdb, bf16* dcolsum, int accumulate_dcol, cudaStream_t stream) {
-    if (dcolsum != nullptr && C > 1024) return -2;
-    if (C % 8) return -1;
-    int sms = llmc_device_sm_count(); if (sms <= 0) sms = 148;
-    int ctas = LNB_CTAS_PER_SM * sms;
-    int rows_per_cta = CEIL_DIV(N, ctas);
-    ctas = CEIL_DIV(N, rows_per_cta);
-    const int nwarps = LNB_WARPS;
-    const size_t big = (size_t)nwarps * 3 * (32 * 4 * 8) * sizeof(float);      // 48 KB: the largest layout (3 arrays, 4 packs per lane)
-    static bool configured = false;
-    auto pick = [&](int maxp, bool acc, bool col) -> decltype(&ln_bwd_fast_kernel<true, 3, true>) {
-        if (maxp == 3) return acc ? (col ? ln_bwd_fast_kernel<true, 3, true> : ln_bwd_fast_kernel<true, 3, false>)
-                                  : (col ? ln_bwd_fast_kernel<false, 3, true> : ln_bwd_fast_kernel<false, 3, false>);
-        return acc ? (col ? ln_bwd_fast_kernel<true, 4, true> : ln_bwd_fast_kernel<true, 4, false>)
-                   : (col ? ln_bwd_fast_kernel<false, 4, true> : ln_bwd_fast_kernel<false, 4, false>);
-    };
-    if (!configured) {
-        for (int mp = 3; mp <= 4; mp++)
-            for (int acc = 0; acc < 2; acc++)
-                for (int col = 0; col < 2; col++)
-                    CUDA_CHECK(cudaFuncSetAttribute(pick(mp, acc, col), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)big));
-        CUDA_CHECK(cudaFuncSetAttribute(ln_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)big));
-        CUDA_CHECK(cudaFuncSetAttribute(ln_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)big));
-        configured = true;
-    }
-    if (C <= 1024) {
-        const int maxp = (C <= 768) ? 3 : 4;
-        const int narr = dcolsum ? 3 : 2;
-        const size_t smem = (size_t)nwarps * narr * maxp * 2 * 32 * sizeof(float4);
-        pick(maxp, accumulate_dinp != 0, dcolsum != nullptr)<<<ctas, nwarps * 32, smem, stream>>>(dinp, scratch, dout, inp, weight, mean, rstd, N, C, rows_per_cta);
-    } else {
-        auto kfn = accumulate_dinp ? ln_bwd_kernel<true> : ln_bwd_kernel<false>;
-        kfn<<<ctas, nwarps * 32, (size_t)nwarps * 2 * (32 * 4 * 8) * sizeof(float), stream>>>(dinp, scratch, dout, inp, weight, mean, rstd, N, C, rows_per_cta);
-    }
-    CUDA_CHECK(cudaGetLastError());
-    ln_bwd_fold_kernel<<<CEIL_DIV(C, 128), 128, 0, stream>>>(dweight, dbias, dcolsum, scratch, ctas, C, accumulate_dwdb, accumulate_dcol);
+    if (C % 8 || C > LNB_MAX_THREADS * 8 * 8) return -1;
+    const int npack = C / 8;
+    const int threads = npack <= LNB_MAX_THREADS ? CEIL_DIV(npack, 32) * 32 : LNB_MAX_THREADS;
+    const int packs = CEIL_DIV(npack, threads);
+    const bool acc = accumulate_dinp != 0, col = dcolsum != nullptr;
+    int ctas = 0, rc;
+    if (packs <= 1) rc = lnb_dispatch<1>(acc, col, dinp, scratch, dout, inp, weight, mean, rstd, N, C, threads, &ctas, stream);
+    else if (packs <= 2) rc = lnb_dispatch<2>(acc, col, dinp, scratch, dout, inp, weight, mean, rstd, N, C, threads, &ctas, stream);
+    else if (packs <= 4) rc = lnb_dispatch<4>(acc, col, dinp, scratch, dout, inp, weight, mean, rstd, N, C, threads, &ctas, stream);
+    else rc = lnb_dispatch<8>(acc, col, dinp, scratch, dout, inp, weight, mean, rstd, N, C, threads, &ctas, stream);
+    if (rc) return rc;
+    ln_bwd_fold_kernel<<<CEIL_DIV(C, 32), 256, 0, stream>>>(dweight, dbias, dcolsum, scratch, ctas, C, accumulate_dwdb, accumulate_dcol);
     CUDA_CHECK(cudaGetLastError());
     return 0;
 }

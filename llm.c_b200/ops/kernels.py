@@ -164,13 +164,10 @@ def layernorm_backward(dinp, dweight, dbias, dout, inp, weight, mean, rstd, accu
     lib = _lib.cuda()
     N, C = inp.shape
     s = _scratch.get("ln_bwd", lib.llmc_layernorm_bwd_scratch(N, C), torch.float32, inp.device)
-    fused_col = dcolsum is not None and C <= 1024
     _launches += 2
     check(lib.llmc_layernorm_bwd(_p(dinp), _p(dweight), _p(dbias), _p(s), _p(dout), _p(inp), _p(weight), _p(mean), _p(rstd),
-                                 N, C, int(accumulate_dinp), int(accumulate_dwdb), _p(dcolsum if fused_col else None),
-                                 int(accumulate_dcol), _stream()), "llmc_layernorm_bwd")
-    if dcolsum is not None and not fused_col:
-        bias_grad(dcolsum, dinp, accumulate=accumulate_dcol)
+                                 N, C, int(accumulate_dinp), int(accumulate_dwdb), _p(dcolsum), int(accumulate_dcol), _stream()),
+          "llmc_layernorm_bwd")
 
 
 def attention_forward(out, lse, qkv, B, T, NH):

@@ -53,8 +53,8 @@ def case(op):
         if op == "attn_fwd":
             return (lambda: K.attention_forward(out, lse, qkv, B, T, NH)), 2.0 * (qkv.numel() + out.numel()), causal
         return (lambda: K.attention_backward(dqkv, dout, qkv, out, lse, B, T, NH)), 2.0 * (2 * qkv.numel() + 2 * out.numel()), 3.5 * causal
-    if op in ("ln_fwd", "fused_residual", "ln_bwd"):
-        N = 131072
+    if op in ("ln_fwd", "fused_residual", "ln_bwd", "ln_bwd_colsum"):
+        N = 65536
         x, y, w, b, dy = _bf(N, C), _bf(N, C), _bf(C) + 1, _bf(C), _bf(N, C)
         out, res = torch.empty_like(x), torch.empty_like(x)
         mean, rstd = torch.empty(N, device=DEV), torch.empty(N, device=DEV)
@@ -64,6 +64,8 @@ def case(op):
             "ln_fwd": (lambda: K.layernorm_forward(out, mean, rstd, x, w, b), 2.0 * 2 * N * C),
             "fused_residual": (lambda: K.fused_residual_forward(res, out, mean, rstd, x, y, w, b), 2.0 * 4 * N * C),
             "ln_bwd": (lambda: K.layernorm_backward(dx, dw, db, dy, x, w, mean, rstd, True, True), 2.0 * 4 * N * C),
+            "ln_bwd_colsum": (lambda: K.layernorm_backward(dx, dw, db, dy, x, w, mean, rstd, True, True, dcolsum=b, accumulate_dcol=False),
+                              2.0 * 4 * N * C),
         }
         fn, bytes_ = fns[op]
         return fn, bytes_, 0.0
@@ -101,7 +103,7 @@ def case(op):
     raise SystemExit("unknown operator %r" % op)
 
 
-OPS = ["gemm_fwd", "gemm_gelu", "gemm_dgrad", "gemm_dgelu", "gemm_wgrad", "attn_fwd", "attn_bwd", "ln_fwd", "fused_residual", "ln_bwd",
+OPS = ["gemm_fwd", "gemm_gelu", "gemm_dgrad", "gemm_dgelu", "gemm_wgrad", "attn_fwd", "attn_bwd", "ln_fwd", "fused_residual", "ln_bwd", "ln_bwd_colsum",
        "classifier", "encoder_fwd", "encoder_bwd", "adamw", "norm", "bias_grad", "gelu"]
 
 

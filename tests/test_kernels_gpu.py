@@ -108,7 +108,7 @@ def test_bias_grad():
     close(db, ref, 5e-2, 1e-2, "bias_grad")
 
 
-@pytest.mark.parametrize("N,C", [(64, 64), (300, 768), (128, 1600), (32, 2048 + 512)])
+@pytest.mark.parametrize("N,C", [(64, 64), (300, 768), (1031, 768), (128, 1600), (32, 2048 + 512), (257, 4096), (40, 8192)])
 def test_layernorm_forward_backward(N, C):
     x, w, b, dy = rnd(N, C), rnd(C) + 1.0, rnd(C), rnd(N, C)
     out = torch.empty(N, C, dtype=torch.bfloat16, device=DEV)
