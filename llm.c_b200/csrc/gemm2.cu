@@ -27,11 +27,12 @@ constexpr int EPI_GROUPS = 4;          // epilogue groups of four warps, each ow
 constexpr int GROUP_COLS = BN / EPI_GROUPS;
 constexpr int EPI_COLS = 32;
 constexpr int EPI_BUF_BYTES = BM * EPI_COLS * 2;      // 8 KB
-// Staging: two 8 KB buffers per epilogue group next to five pipeline stages.  STORE alternates between them; the epilogues
-// with two tensors per chunk (GELU: activation + pre-activation out; dGELU: pre-activation in + gradient out) use one each.
+// Staging: 64 KB next to five pipeline stages, split evenly over the sixteen epilogue warps (two 2 KB buffers each).  STORE
+// alternates between a warp's two buffers; the epilogues with two tensors per chunk (GELU: activation + pre-activation out;
+// dGELU: pre-activation in + gradient out) use one each.
 __host__ __device__ constexpr int stages_for(int mode) { return 5; }
 __host__ __device__ constexpr int epi_bufs_for(int mode) { return 2 * EPI_GROUPS; }
-__host__ __device__ constexpr int smem_for(int mode) { return stages_for(mode) * STAGE_BYTES + epi_bufs_for(mode) * EPI_BUF_BYTES + 1024 + 256; }
+__host__ __device__ constexpr int smem_for(int mode) { return stages_for(mode) * STAGE_BYTES + epi_bufs_for(mode) * EPI_BUF_BYTES + 1024 + 512; }
 constexpr int NUM_THREADS = 576;       // TMA warp + MMA warp + 16 epilogue warps
 constexpr int TMEM_COLS = 512;
 constexpr int RASTER_GROUP = 8;       // in units of 256-row tiles
@@ -53,7 +54,6 @@ struct Gemm2Args {
 
 DEVINL void epi_barrier() { asm volatile("bar.sync 1, 512;" ::: "memory"); }
 
-DEVINL void group_barrier(int grp) { asm volatile("bar.sync %0, 128;" ::"r"(2 + grp) : "memory"); }
 DEVINL bool epi_any(int pred) {
     uint32_t r;
     asm volatile(
@@ -114,8 +114,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     uint64_t* empty = bars + STAGES;          // [STAGES]  one per CTA, raised by the leader's multicast commit
     uint64_t* acc_full = bars + 2 * STAGES;   // [2]       one per CTA, raised by the leader's multicast commit
     uint64_t* acc_empty = acc_full + 2;       // [2]       used in the leader CTA: all epilogue warps of the pair arrive
-    uint64_t* aux_full = acc_empty + 2;       // [EPI_GROUPS]  (EPI_DGELU)
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aux_full + EPI_GROUPS);
+    uint64_t* aux_full = acc_empty + 2;       // [4 * EPI_GROUPS]  one per epilogue warp (EPI_DGELU)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(aux_full + 4 * EPI_GROUPS);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     int* last_flag = const_cast<int*>(abort_flag) + 1;
 
@@ -127,7 +127,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
         for (int b = 0; b < 2; b++) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 2 * 4 * EPI_GROUPS); }
-        for (int b = 0; b < EPI_GROUPS; b++) mbar_init(&aux_full[b], 1);
+        for (int b = 0; b < 4 * EPI_GROUPS; b++) mbar_init(&aux_full[b], 1);
         *abort_flag = 0;
         mbar_fence_init();
     }
@@ -230,28 +230,32 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         const int grp = ew >> 2;
         const int q = warp & 3;
         const int row = q * 32 + lane;
-        const bool leader = ((ew & 3) == 0) && lane == 0;
-        // this group's two staging buffers
-        constexpr int BUFS_PER_GROUP = NUM_EPI_BUFS / EPI_GROUPS;
-        uint8_t* gbuf = epi_smem + grp * BUFS_PER_GROUP * EPI_BUF_BYTES;
+        // Every epilogue warp is its own pipeline over its 32 rows x GROUP_COLS columns: TMEM -> registers -> its own two
+        // 2 KB staging buffers (64-byte swizzle) -> its own TMA stores.  Warps never wait for one another, so the TMEM
+        // load, shared-memory fence and store-drain latencies of one warp are covered by the other three of its scheduler.
+        //   STORE: the two buffers alternate;  GELU: buffer 0 = activation, buffer 1 = pre-activation;
+        //   DGELU: buffer 0 = output, buffer 1 = this warp's 32 x 32 box of the stored pre-activation (TMA load).
+        constexpr int WARP_BUF_BYTES = 32 * EPI_COLS * 2;           // 2 KB
+        static_assert(2 * WARP_BUF_BYTES * 4 * EPI_GROUPS == NUM_EPI_BUFS * EPI_BUF_BYTES, "staging space is split evenly over the epilogue warps");
+        uint8_t* wbuf = epi_smem + ew * 2 * WARP_BUF_BYTES;
         constexpr int CHUNKS = GROUP_COLS / EPI_COLS;
-        const int swz = (row >> 1) & 3;
+        const int swz = (lane >> 1) & 3;
         uint32_t kctr = 0;
         const bool store_thread = (threadIdx.x == 64);
-        // pre-activation chunk -> this group's second buffer (EPI_DGELU); chunk k completes phase k & 1 of the group's barrier
+        // pre-activation box of chunk c_ of work item w_ -> this warp's second buffer; chunk k completes phase k & 1 of its barrier
         auto aux_load = [&](int w_, int c_) {
             int mt_, nt_, sp_; decode(w_, mt_, nt_, sp_);
-            uint64_t* bar = &aux_full[grp];
-            mbar_expect_tx(bar, EPI_BUF_BYTES);
-            tma_load_2d(gbuf + EPI_BUF_BYTES, &tmAux, bar, nt_ * BN + grp * GROUP_COLS + c_ * EPI_COLS, mt_ * 256 + (int)rank * BM);
+            uint64_t* bar = &aux_full[ew];
+            mbar_expect_tx(bar, WARP_BUF_BYTES);
+            tma_load_2d(wbuf + WARP_BUF_BYTES, &tmAux, bar, nt_ * BN + grp * GROUP_COLS + c_ * EPI_COLS, mt_ * 256 + (int)rank * BM + q * 32);
         };
-        // (work item, chunk) that follows (w_, c_) in this group's sequence; false at the end
+        // (work item, chunk) that follows (w_, c_) in this warp's sequence; false at the end
         auto next_chunk = [&](int& w_, int& c_) {
             if (c_ + 1 < CHUNKS) { c_++; return true; }
             if (w_ + npairs < total_work) { w_ += npairs; c_ = 0; return true; }
             return false;
         };
-        if (MODE == EPI_DGELU && leader && pair < total_work) aux_load(pair, 0);
+        if (MODE == EPI_DGELU && lane == 0 && pair < total_work) aux_load(pair, 0);
         const uint32_t lead_acc_empty0 = map_to_cta(smem_u32(&acc_empty[0]), 0);
         const uint32_t lead_acc_empty1 = map_to_cta(smem_u32(&acc_empty[1]), 0);
         int it = 0;
@@ -379,6 +383,12 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                 uint32_t v[32];
                 tmem_ld32(t_row + c * EPI_COLS, v);
                 tmem_ld_wait();
+                if (c == CHUNKS - 1) {
+                    // this warp holds the last of its part of the accumulator: tell the leader CTA's MMA thread
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(lead_acc_empty);
+                }
                 float* f = reinterpret_cast<float*>(v);
                 if ((MODE == EPI_STORE || MODE == EPI_GELU) && g.bias != nullptr) {
                     #pragma unroll
@@ -390,20 +400,13 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                         }
                     }
                 }
-                // buffers of this chunk
-                uint8_t* out_buf; uint8_t* aux_buf = nullptr;
-                if (MODE == EPI_STORE) {
-                    out_buf = gbuf + (kctr & 1) * EPI_BUF_BYTES;
-                    if (leader) tma_store_wait_read<1>();      // the store issued two chunks ago has read this buffer
-                } else {
-                    out_buf = gbuf;
-                    aux_buf = gbuf + EPI_BUF_BYTES;
-                    if (leader) tma_store_wait_read<0>();
-                }
-                uint8_t* out_row = out_buf + row * 64;
-                uint8_t* aux_row = aux_buf + row * 64;
+                uint8_t* out_buf = wbuf + ((MODE == EPI_STORE) ? (kctr & 1) * WARP_BUF_BYTES : 0);
+                uint8_t* aux_buf = wbuf + WARP_BUF_BYTES;
+                uint8_t* out_row = out_buf + lane * 64;
+                uint8_t* aux_row = aux_buf + lane * 64;
+                uint4 pre_q[4], out_q[4];
                 if (MODE == EPI_DGELU) {
-                    ok = mbar_wait(&aux_full[grp], kctr & 1, abort_flag, g.status, 0xC40 + grp) && ok;
+                    ok = mbar_wait(&aux_full[ew], kctr & 1, abort_flag, g.status, 0xC40 + ew) && ok;
                     #pragma unroll
                     for (int j = 0; j < 4; j++) {
                         const uint4 a = *reinterpret_cast<const uint4*>(aux_row + ((j ^ swz) * 16));
@@ -413,50 +416,48 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                         f[j*8+4] *= gelu_grad_fast(a2.x); f[j*8+5] *= gelu_grad_fast(a2.y);
                         f[j*8+6] *= gelu_grad_fast(a3.x); f[j*8+7] *= gelu_grad_fast(a3.y);
                     }
-                }
-                group_barrier(grp);      // output buffer is free; (DGELU) everybody has read this pre-activation chunk
-                if (MODE == EPI_DGELU && leader) {
-                    // refill the buffer just consumed with the next chunk's pre-activation
-                    int w_ = w, c_ = c;
-                    if (next_chunk(w_, c_)) aux_load(w_, c_);
-                }
-                if (MODE == EPI_GELU) {
-                    #pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        uint4 pre, post;
-                        pre.x = pack_bf16x2(f[j*8+0], f[j*8+1]); pre.y = pack_bf16x2(f[j*8+2], f[j*8+3]);
-                        pre.z = pack_bf16x2(f[j*8+4], f[j*8+5]); pre.w = pack_bf16x2(f[j*8+6], f[j*8+7]);
-                        const float2 r0 = unpack_bf16x2(pre.x), r1 = unpack_bf16x2(pre.y), r2 = unpack_bf16x2(pre.z), r3 = unpack_bf16x2(pre.w);
-                        post.x = pack_bf16x2(gelu_fast(r0.x), gelu_fast(r0.y)); post.y = pack_bf16x2(gelu_fast(r1.x), gelu_fast(r1.y));
-                        post.z = pack_bf16x2(gelu_fast(r2.x), gelu_fast(r2.y)); post.w = pack_bf16x2(gelu_fast(r3.x), gelu_fast(r3.y));
-                        *reinterpret_cast<uint4*>(aux_row + ((j ^ swz) * 16)) = pre;
-                        *reinterpret_cast<uint4*>(out_row + ((j ^ swz) * 16)) = post;
+                    __syncwarp();            // every lane has read its row of the pre-activation box
+                    if (lane == 0) {
+                        int w_ = w, c_ = c;
+                        if (next_chunk(w_, c_)) aux_load(w_, c_);
                     }
-                } else {
-                    #pragma unroll
-                    for (int j = 0; j < 4; j++) {
-                        uint4 o;
-                        o.x = pack_bf16x2(f[j*8+0], f[j*8+1]); o.y = pack_bf16x2(f[j*8+2], f[j*8+3]);
-                        o.z = pack_bf16x2(f[j*8+4], f[j*8+5]); o.w = pack_bf16x2(f[j*8+6], f[j*8+7]);
-                        *reinterpret_cast<uint4*>(out_row + ((j ^ swz) * 16)) = o;
+                }
+                // all arithmetic happens before the wait for the staging buffer, so the drain of the previous store hides under it
+                #pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    uint4 o;
+                    o.x = pack_bf16x2(f[j*8+0], f[j*8+1]); o.y = pack_bf16x2(f[j*8+2], f[j*8+3]);
+                    o.z = pack_bf16x2(f[j*8+4], f[j*8+5]); o.w = pack_bf16x2(f[j*8+6], f[j*8+7]);
+                    if (MODE == EPI_GELU) {
+                        pre_q[j] = o;
+                        const float2 r0 = unpack_bf16x2(o.x), r1 = unpack_bf16x2(o.y), r2 = unpack_bf16x2(o.z), r3 = unpack_bf16x2(o.w);
+                        o.x = pack_bf16x2(gelu_fast(r0.x), gelu_fast(r0.y)); o.y = pack_bf16x2(gelu_fast(r1.x), gelu_fast(r1.y));
+                        o.z = pack_bf16x2(gelu_fast(r2.x), gelu_fast(r2.y)); o.w = pack_bf16x2(gelu_fast(r3.x), gelu_fast(r3.y));
                     }
+                    out_q[j] = o;
+                }
+                if (lane == 0) {
+                    if (MODE == EPI_STORE) tma_store_wait_read<1>();      // the store issued two chunks ago has read this buffer
+                    else tma_store_wait_read<0>();
+                }
+                __syncwarp();
+                #pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    *reinterpret_cast<uint4*>(out_row + ((j ^ swz) * 16)) = out_q[j];
+                    if (MODE == EPI_GELU) *reinterpret_cast<uint4*>(aux_row + ((j ^ swz) * 16)) = pre_q[j];
                 }
                 fence_async_smem();
-                group_barrier(grp);
-                if (leader && ok && col0 < g.N) {
-                    tma_store_2d(&tmD, out_buf, col0, m0);
-                    if (MODE == EPI_GELU) tma_store_2d(&tmAux, aux_buf, col0, m0);
+                __syncwarp();
+                if (lane == 0 && ok && col0 < g.N) {
+                    tma_store_2d(&tmD, out_buf, col0, m0 + q * 32);
+                    if (MODE == EPI_GELU) tma_store_2d(&tmAux, aux_buf, col0, m0 + q * 32);
                     tma_store_commit();
                 }
                 kctr++;
             }
-            // this warp has read its part of the accumulator: tell the leader CTA's MMA thread
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(lead_acc_empty);
             if (epi_any(*abort_flag)) break;
         }
-        if (leader) tma_store_wait<0>();
+        if (lane == 0) tma_store_wait<0>();
     }
 
     // teardown: the pair meets (nobody may still signal a barrier of a CTA that has left), then TMEM is freed
@@ -548,7 +549,7 @@ extern "C" int llmc_gemm2(const bf16* A, const bf16* B, bf16* D, const bf16* bia
     }
     {
         uint64_t dims[2] = {(uint64_t)N, (uint64_t)M}, strides[2] = {2, (uint64_t)ldd * 2};
-        uint32_t box[2] = {EPI_COLS, BM};
+        uint32_t box[2] = {EPI_COLS, 32};        // one epilogue warp's rows
         if ((rc = llmc_get_tensormap(&tmD, D, 2, 2, dims, strides, box, 2))) return rc;
         tmAux = tmD;
         if (mode == EPI_GELU || mode == EPI_DGELU) { if ((rc = llmc_get_tensormap(&tmAux, aux, 2, 2, dims, strides, box, 2))) return rc; }
