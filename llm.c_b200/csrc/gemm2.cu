@@ -422,36 +422,54 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                         if (next_chunk(w_, c_)) aux_load(w_, c_);
                     }
                 }
-                // all arithmetic happens before the wait for the staging buffer, so the drain of the previous store hides under it
-                #pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    uint4 o;
-                    o.x = pack_bf16x2(f[j*8+0], f[j*8+1]); o.y = pack_bf16x2(f[j*8+2], f[j*8+3]);
-                    o.z = pack_bf16x2(f[j*8+4], f[j*8+5]); o.w = pack_bf16x2(f[j*8+6], f[j*8+7]);
-                    if (MODE == EPI_GELU) {
-                        pre_q[j] = o;
-                        const float2 r0 = unpack_bf16x2(o.x), r1 = unpack_bf16x2(o.y), r2 = unpack_bf16x2(o.z), r3 = unpack_bf16x2(o.w);
-                        o.x = pack_bf16x2(gelu_fast(r0.x), gelu_fast(r0.y)); o.y = pack_bf16x2(gelu_fast(r1.x), gelu_fast(r1.y));
-                        o.z = pack_bf16x2(gelu_fast(r2.x), gelu_fast(r2.y)); o.w = pack_bf16x2(gelu_fast(r3.x), gelu_fast(r3.y));
+                if (MODE == EPI_GELU) {
+                    // Two stores per chunk, each from its own buffer and in its own bulk group, issued half a chunk apart:
+                    // when a buffer is needed again the only younger group is the other tensor's, so each store has a full
+                    // chunk of work to drain underneath (the same slack the alternating buffers give plain STORE).
+                    #pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        pre_q[j].x = pack_bf16x2(f[j*8+0], f[j*8+1]); pre_q[j].y = pack_bf16x2(f[j*8+2], f[j*8+3]);
+                        pre_q[j].z = pack_bf16x2(f[j*8+4], f[j*8+5]); pre_q[j].w = pack_bf16x2(f[j*8+6], f[j*8+7]);
                     }
-                    out_q[j] = o;
-                }
-                if (lane == 0) {
-                    if (MODE == EPI_STORE) tma_store_wait_read<1>();      // the store issued two chunks ago has read this buffer
-                    else tma_store_wait_read<0>();
-                }
-                __syncwarp();
-                #pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    *reinterpret_cast<uint4*>(out_row + ((j ^ swz) * 16)) = out_q[j];
-                    if (MODE == EPI_GELU) *reinterpret_cast<uint4*>(aux_row + ((j ^ swz) * 16)) = pre_q[j];
-                }
-                fence_async_smem();
-                __syncwarp();
-                if (lane == 0 && ok && col0 < g.N) {
-                    tma_store_2d(&tmD, out_buf, col0, m0 + q * 32);
-                    if (MODE == EPI_GELU) tma_store_2d(&tmAux, aux_buf, col0, m0 + q * 32);
-                    tma_store_commit();
+                    if (lane == 0) tma_store_wait_read<1>();
+                    __syncwarp();
+                    #pragma unroll
+                    for (int j = 0; j < 4; j++) *reinterpret_cast<uint4*>(aux_row + ((j ^ swz) * 16)) = pre_q[j];
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0 && ok && col0 < g.N) { tma_store_2d(&tmAux, aux_buf, col0, m0 + q * 32); tma_store_commit(); }
+                    #pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        // the activation is computed from the rounded pre-activation, so a later recomputation from the stored
+                        // tensor gives the same bits
+                        const float2 r0 = unpack_bf16x2(pre_q[j].x), r1 = unpack_bf16x2(pre_q[j].y), r2 = unpack_bf16x2(pre_q[j].z), r3 = unpack_bf16x2(pre_q[j].w);
+                        out_q[j].x = pack_bf16x2(gelu_fast(r0.x), gelu_fast(r0.y)); out_q[j].y = pack_bf16x2(gelu_fast(r1.x), gelu_fast(r1.y));
+                        out_q[j].z = pack_bf16x2(gelu_fast(r2.x), gelu_fast(r2.y)); out_q[j].w = pack_bf16x2(gelu_fast(r3.x), gelu_fast(r3.y));
+                    }
+                    if (lane == 0) tma_store_wait_read<1>();
+                    __syncwarp();
+                    #pragma unroll
+                    for (int j = 0; j < 4; j++) *reinterpret_cast<uint4*>(out_row + ((j ^ swz) * 16)) = out_q[j];
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0 && ok && col0 < g.N) { tma_store_2d(&tmD, out_buf, col0, m0 + q * 32); tma_store_commit(); }
+                } else {
+                    // all arithmetic happens before the wait for the staging buffer, so the drain of the previous store hides under it
+                    #pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        out_q[j].x = pack_bf16x2(f[j*8+0], f[j*8+1]); out_q[j].y = pack_bf16x2(f[j*8+2], f[j*8+3]);
+                        out_q[j].z = pack_bf16x2(f[j*8+4], f[j*8+5]); out_q[j].w = pack_bf16x2(f[j*8+6], f[j*8+7]);
+                    }
+                    if (lane == 0) {
+                        if (MODE == EPI_STORE) tma_store_wait_read<1>();      // the store issued two chunks ago has read this buffer
+                        else tma_store_wait_read<0>();
+                    }
+                    __syncwarp();
+                    #pragma unroll
+                    for (int j = 0; j < 4; j++) *reinterpret_cast<uint4*>(out_row + ((j ^ swz) * 16)) = out_q[j];
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0 && ok && col0 < g.N) { tma_store_2d(&tmD, out_buf, col0, m0 + q * 32); tma_store_commit(); }
                 }
                 kctr++;
             }
