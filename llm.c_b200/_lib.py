@@ -40,12 +40,14 @@ def cuda():
         return _cuda
     lib = _load("libllmc_b200.so", "build_cuda")
     P, I, L, F, U, S = c_void_p, c_int, c_longlong, c_float, c_uint, c_void_p
+    U64 = ctypes.c_ulonglong
     sigs = {
         "llmc_status_read": (I, [I, POINTER(c_uint)]),
         "llmc_tensormap_cache_clear": (None, []),
         "llmc_device_sm_count": (I, []),
         "llmc_gemm": (I, [P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, P, I, S]),
         "llmc_gemm2": (I, [P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, P, S]),
+        "llmc_gemm2_after_flags": (I, [P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, P, P, I, U64, S]),
         "llmc_gemm2_workspace": (None, [I, I, I, POINTER(c_longlong), POINTER(c_int)]),
         "llmc_gemm2_pick_splits": (I, [I, I, I, I]),
         "llmc_gemm_workspace": (None, [I, I, I, POINTER(c_longlong), POINTER(c_int)]),

@@ -65,8 +65,8 @@ def main():
         seq[1] += 1
         _lib.check(lib.llmc_p2p_allreduce_scalar(c_s, ctypes.c_void_p(norm_sq.data_ptr()), r, N, seq[1], stream), "ar")
         _lib.check(lib.llmc_p2p_adamw_allgather(c_p, c_s, kernels._p(master), kernels._p(grads), kernels._p(m), kernels._p(v), ctypes.byref(tab), r, N,
-                                                6e-4, 0.9, 0.95, 1e-8, 1, 1.0, kernels._p(norm_sq), 1.0, seq[0], kernels._p(counter), ctas, stream), "adamw_ag")
-        _lib.check(lib.llmc_p2p_wait(c_s, r, N, 0, seq[0], stream), "wait")
+                                                6e-4, 0.9, 0.95, 1e-8, 1, 1.0, kernels._p(norm_sq), 1.0, seq[0], kernels._p(counter), ctas, 0, stream), "adamw_ag")
+        _lib.check(lib.llmc_p2p_wait(c_s, r, N, 0, 0, seq[0], stream), "wait")
 
     def step_nccl():
         for i in range(slices):

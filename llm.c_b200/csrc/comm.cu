@@ -18,9 +18,13 @@
 //                   every peer's signal buffer and sums the N slots in rank order.
 //  adamw_allgather  AdamW + stochastic rounding on the own shards; each rounded bf16 pack is stored to
 //                   the own parameter buffer and to every peer's (16-byte peer stores), the last CTA to
-//                   finish raises this rank's "parameters published" flag on all peers.
+//                   finish raises this rank's "parameters published" flag of the launch's channel on all
+//                   peers.  The caller launches it once per parameter group in the order the forward pass
+//                   consumes the groups; the consumer is the first GEMM that reads a group's weights (its
+//                   TMA producer polls the group's flags before its first load, see gemm2.cu), so the forward
+//                   pass of early layers runs while later groups are still being updated and gathered.
 //                   Replaces adamw_kernel3 + ncclAllGather (train_gpt2.cu:1101-1120 of the reference).
-//  wait_flags       tiny kernel the consumer stream runs before it first reads gathered parameters.
+//  wait_flags       tiny kernel for consumers that are not GEMMs (embedding lookup, checkpoint writer).
 #include "common.cuh"
 
 struct TensorView {        // same layout as in optim.cu
@@ -51,10 +55,11 @@ struct SliceList {
 
 // signal buffer layout (64-bit words)
 constexpr int SIG_RS_BASE = 0;          // [channel 0..199][src rank]
-constexpr int SIG_AG = 200 * MAX_RANKS; // [src rank]
-constexpr int SIG_BARRIER = 201 * MAX_RANKS;
-constexpr int SIG_SCALAR = 202 * MAX_RANKS;     // [parity][src rank] packed {seq, float}
-constexpr int SIG_WORDS = 208 * MAX_RANKS;
+constexpr int SIG_AG_BASE = 200 * MAX_RANKS;    // [channel 0..199][src rank]  "parameters of this group are published"
+constexpr int SIG_BARRIER = 400 * MAX_RANKS;
+constexpr int SIG_SCALAR = 401 * MAX_RANKS;     // [parity][src rank] packed {seq, float}
+constexpr int SIG_WORDS = 408 * MAX_RANKS;
+constexpr int MAX_CHANNELS = 200;
 
 // limit of every peer-flag wait in clock cycles; adjustable at run time (tests shorten it)
 __device__ long long g_flag_wait_cycles = FLAG_WAIT_CYCLES;
@@ -173,7 +178,7 @@ adamw_allgather_kernel(PeerPtrs params, PeerPtrs sig, float* __restrict__ master
                        float* __restrict__ m_buf, float* __restrict__ v_buf, const TensorTable tab, int rank, int N,
                        float lr, float beta1, float beta2, float bc1, float bc2, float eps, float grad_scale,
                        const float* __restrict__ norm_sq, float grad_clip, unsigned long long seq,
-                       unsigned int* __restrict__ done_counter) {
+                       unsigned int* __restrict__ done_counter, int channel) {
     float scale = grad_scale;
     bool skip = false;
     if (norm_sq != nullptr) {
@@ -209,7 +214,7 @@ adamw_allgather_kernel(PeerPtrs params, PeerPtrs sig, float* __restrict__ master
                     vv = fmaf(beta2, vv, (1.0f - beta2) * gg * gg);
                     const float mh = mm / bc1, vh = vv / bc2;
                     ww = ww - lr * (mh / (sqrtf(vh) + eps) + tv.wd * ww);
-                    out[e] = stochastic_round_bf16(ww, squirrel_noise5(sr_position(pk * 8 + e, (int)l), tv.seed));
+                    out[e] = stochastic_round_bf16(ww, squirrel_noise5(sr_position(pk * 8 + e, (int)l + tv.pad), tv.seed));
                 }
                 st128(m_buf + oi, m0); st128(m_buf + oi + 4, m1); st128(v_buf + oi, v0); st128(v_buf + oi + 4, v1);
                 if (HAS_MASTER) { st128(master + oi, w0); st128(master + oi + 4, w1); }
@@ -234,7 +239,7 @@ adamw_allgather_kernel(PeerPtrs params, PeerPtrs sig, float* __restrict__ master
     if (last && threadIdx.x < N) {
         __threadfence_system();
         unsigned long long* peer = reinterpret_cast<unsigned long long*>(sig.p[threadIdx.x]);
-        st_release_sys(peer + SIG_AG + rank, seq);
+        st_release_sys(peer + SIG_AG_BASE + channel * MAX_RANKS + rank, seq);
     }
 }
 
@@ -262,9 +267,13 @@ int fill(PeerPtrs* pp, const unsigned long long* ptrs, int N) {
 extern "C" int llmc_p2p_signal_words() { return SIG_WORDS; }
 
 // Sets the limit (clock cycles) after which a wait on a peer flag gives up and records ST_FLAG_TIMEOUT. 0 restores the default.
+static long long h_flag_wait_cycles = FLAG_WAIT_CYCLES;      // host mirror, for kernels of other files that take the limit as an argument
+long long llmc_p2p_wait_cycles_host() { return h_flag_wait_cycles; }
+
 extern "C" int llmc_p2p_set_wait_cycles(long long cycles) {
     long long v = cycles > 0 ? cycles : FLAG_WAIT_CYCLES;
     CUDA_CHECK(cudaMemcpyToSymbol(g_flag_wait_cycles, &v, sizeof(v)));
+    h_flag_wait_cycles = v;
     return 0;
 }
 
@@ -294,22 +303,29 @@ extern "C" int llmc_p2p_allreduce_scalar(const unsigned long long* sig_ptrs, flo
 extern "C" int llmc_p2p_adamw_allgather(const unsigned long long* param_ptrs, const unsigned long long* sig_ptrs, float* master,
                                         const bf16* grads, float* m, float* v, const TensorTable* tab, int rank, int N,
                                         float lr, float beta1, float beta2, float eps, int t, float grad_scale, const float* norm_sq,
-                                        float grad_clip, unsigned long long seq, unsigned int* done_counter, int ctas, cudaStream_t stream) {
+                                        float grad_clip, unsigned long long seq, unsigned int* done_counter, int ctas, int channel,
+                                        cudaStream_t stream) {
     PeerPtrs p, s;
     if (fill(&p, param_ptrs, N) || fill(&s, sig_ptrs, N)) return -1;
+    if (channel < 0 || channel >= MAX_CHANNELS) return -3;
     for (int i = 0; i < tab->count; i++) if (tab->t[i].n % 8 || tab->t[i].p_base % 8 || tab->t[i].p_stride % 8 || tab->t[i].o_base % 8 || tab->t[i].o_stride % 8) return -2;
     const float bc1 = 1.0f - powf(beta1, (float)t), bc2 = 1.0f - powf(beta2, (float)t);
-    if (master) adamw_allgather_kernel<true><<<ctas, 512, 0, stream>>>(p, s, master, grads, m, v, *tab, rank, N, lr, beta1, beta2, bc1, bc2, eps, grad_scale, norm_sq, grad_clip, seq, done_counter);
-    else adamw_allgather_kernel<false><<<ctas, 512, 0, stream>>>(p, s, master, grads, m, v, *tab, rank, N, lr, beta1, beta2, bc1, bc2, eps, grad_scale, norm_sq, grad_clip, seq, done_counter);
+    if (master) adamw_allgather_kernel<true><<<ctas, 512, 0, stream>>>(p, s, master, grads, m, v, *tab, rank, N, lr, beta1, beta2, bc1, bc2, eps, grad_scale, norm_sq, grad_clip, seq, done_counter, channel);
+    else adamw_allgather_kernel<false><<<ctas, 512, 0, stream>>>(p, s, master, grads, m, v, *tab, rank, N, lr, beta1, beta2, bc1, bc2, eps, grad_scale, norm_sq, grad_clip, seq, done_counter, channel);
     CUDA_CHECK(cudaGetLastError());
     return 0;
 }
 
-// which: 0 = parameters published (all-gather), 1 = barrier
-extern "C" int llmc_p2p_wait(const unsigned long long* sig_ptrs, int rank, int N, int which, unsigned long long seq, cudaStream_t stream) {
+// word offset, inside a rank's signal buffer, of the N "published" flags of a parameter group
+extern "C" int llmc_p2p_ag_flag_offset(int channel) { return SIG_AG_BASE + channel * MAX_RANKS; }
+
+// which: 0 = parameters of `channel` published (all-gather), 1 = barrier
+extern "C" int llmc_p2p_wait(const unsigned long long* sig_ptrs, int rank, int N, int which, int channel, unsigned long long seq,
+                             cudaStream_t stream) {
     PeerPtrs s;
     if (fill(&s, sig_ptrs, N)) return -1;
-    wait_flags_kernel<<<1, 32, 0, stream>>>(s, rank, N, which == 0 ? SIG_AG : SIG_BARRIER, seq, llmc_status_ptr());
+    if (which == 0 && (channel < 0 || channel >= MAX_CHANNELS)) return -3;
+    wait_flags_kernel<<<1, 32, 0, stream>>>(s, rank, N, which == 0 ? SIG_AG_BASE + channel * MAX_RANKS : SIG_BARRIER, seq, llmc_status_ptr());
     CUDA_CHECK(cudaGetLastError());
     return 0;
 }

@@ -50,6 +50,8 @@ struct Gemm2Args {
     unsigned int* counters;                   // one per half tile (tile * 2 + CTA rank), zero before and after the launch
     int accumulate;
     unsigned int* status;
+    // optional: flags in this GPU's memory that peers raise when the B operand (gathered weights) is complete
+    const unsigned long long* wait_flags; int wait_n; unsigned long long wait_seq; long long wait_cycles;
 };
 
 DEVINL void epi_barrier() { asm volatile("bar.sync 1, 512;" ::: "memory"); }
@@ -156,8 +158,25 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
     if (warp == 0) {
         // ---------------- TMA producer (both CTAs; each loads its own halves) ----------------
         if (lane == 0) {
+            if (g.wait_flags != nullptr) {
+                // The weights this GEMM reads are being gathered from the other GPUs: rank r raises flag r (in this GPU's
+                // memory, release at system scope) after its stores have landed.  Bounded polls; on expiry the CTA gives up.
+                bool arrived = true;
+                for (int r = 0; r < g.wait_n && arrived; r++) {
+                    const long long t0 = clock64();
+                    while (true) {
+                        unsigned long long v;
+                        asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(g.wait_flags + r) : "memory");
+                        if (v >= g.wait_seq) break;
+                        if (clock64() - t0 > g.wait_cycles) { record_error(g.status, ST_FLAG_TIMEOUT, 0x9F0 + r); arrived = false; break; }
+                        __nanosleep(200);
+                    }
+                }
+                if (!arrived) *abort_flag = 1;
+                asm volatile("fence.proxy.async.global;" ::: "memory");      // peers' generic-proxy stores before this thread's TMA loads
+            }
             int stage = 0; uint32_t phase = 0;
-            for (int w = pair; w < total_work; w += npairs) {
+            for (int w = pair; w < total_work && !*abort_flag; w += npairs) {
                 int mt, nt, sp; decode(w, mt, nt, sp);
                 const int m0 = mt * 256 + (int)rank * BM;
                 const int n0 = nt * BN + (int)rank * BNH;
@@ -530,9 +549,12 @@ extern "C" int llmc_gemm2_pick_splits(int M, int N, int K, int sm_count) {
 //   a_mn_major = 0: A is [M][K]; 1: A is [K][M].   b_mn_major = 0: B is [N][K]; 1: B is [K][N].
 // mode: 0 store (+bias), 1 GELU (aux receives the pre-activation), 2 dGELU (aux holds the pre-activation),
 //       3 D (+)= result with optional split-K (workspace / counters as sized by llmc_gemm2_workspace).
-extern "C" int llmc_gemm2(const bf16* A, const bf16* B, bf16* D, const bf16* bias, bf16* aux, int M, int N, int K,
-                          int lda, int ldb, int ldd, int a_mn_major, int b_mn_major, int mode, int accumulate, int splits,
-                          float* workspace, unsigned int* counters, cudaStream_t stream) {
+long long llmc_p2p_wait_cycles_host();      // comm.cu: the limit of every peer-flag wait, in clock cycles
+
+static int gemm2_impl(const bf16* A, const bf16* B, bf16* D, const bf16* bias, bf16* aux, int M, int N, int K,
+                      int lda, int ldb, int ldd, int a_mn_major, int b_mn_major, int mode, int accumulate, int splits,
+                      float* workspace, unsigned int* counters, const unsigned long long* wait_flags, int wait_n,
+                      unsigned long long wait_seq, cudaStream_t stream) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     if ((N % 8) || (lda % 8) || (ldb % 8) || (ldd % 8)) return -1;
     Gemm2Args g;
@@ -545,6 +567,7 @@ extern "C" int llmc_gemm2(const bf16* A, const bf16* B, bf16* D, const bf16* bia
     if (g.splits > 1 && (!workspace || !counters)) return -1;
     g.bias = bias; g.D = D; g.ldd = ldd; g.workspace = workspace; g.counters = counters; g.accumulate = accumulate;
     g.status = llmc_status_ptr();
+    g.wait_flags = wait_flags; g.wait_n = wait_n; g.wait_seq = wait_seq; g.wait_cycles = wait_flags ? llmc_p2p_wait_cycles_host() : 0;
     CUtensorMap tmA, tmB, tmD, tmAux;
     int rc;
     if (a_mn_major == 0) {
@@ -589,4 +612,23 @@ extern "C" int llmc_gemm2(const bf16* A, const bf16* B, bf16* D, const bf16* bia
     }
 #undef LAUNCH2
     return -1;
+}
+
+extern "C" int llmc_gemm2(const bf16* A, const bf16* B, bf16* D, const bf16* bias, bf16* aux, int M, int N, int K,
+                          int lda, int ldb, int ldd, int a_mn_major, int b_mn_major, int mode, int accumulate, int splits,
+                          float* workspace, unsigned int* counters, cudaStream_t stream) {
+    return gemm2_impl(A, B, D, bias, aux, M, N, K, lda, ldb, ldd, a_mn_major, b_mn_major, mode, accumulate, splits, workspace, counters,
+                      nullptr, 0, 0, stream);
+}
+
+// The same GEMM as the consumer of an in-flight all-gather: before its first load every CTA polls `wait_n` 64-bit flags at
+// `wait_flags` (this GPU's memory; rank r's flag is raised by rank r once its shards of the operand have been stored here)
+// until they reach `wait_seq`.  The forward pass of early layers then overlaps the update and gather of later ones.
+extern "C" int llmc_gemm2_after_flags(const bf16* A, const bf16* B, bf16* D, const bf16* bias, bf16* aux, int M, int N, int K,
+                                      int lda, int ldb, int ldd, int a_mn_major, int b_mn_major, int mode, int accumulate, int splits,
+                                      float* workspace, unsigned int* counters, const unsigned long long* wait_flags, int wait_n,
+                                      unsigned long long wait_seq, cudaStream_t stream) {
+    if (wait_flags == nullptr || wait_n < 1 || wait_n > 8) return -1;
+    return gemm2_impl(A, B, D, bias, aux, M, N, K, lda, ldb, ldd, a_mn_major, b_mn_major, mode, accumulate, splits, workspace, counters,
+                      wait_flags, wait_n, wait_seq, stream);
 }

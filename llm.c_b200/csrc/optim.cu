@@ -90,7 +90,7 @@ adamw_kernel(bf16* __restrict__ params, float* __restrict__ master, const bf16* 
         const float mh = m / bc1, vh = v / bc2;
         const float old = HAS_MASTER ? master[oi] : __bfloat162float(params[pi]);
         const float p = old - lr * (mh / (sqrtf(vh) + eps) + tv.wd * old);
-        params[pi] = stochastic_round_bf16(p, squirrel_noise5(sr_position(idx, (int)l), tv.seed));
+        params[pi] = stochastic_round_bf16(p, squirrel_noise5(sr_position(idx, (int)l + tv.pad), tv.seed));
         if (HAS_MASTER) master[oi] = p;
     }
 }
@@ -103,7 +103,7 @@ from_master_kernel(bf16* __restrict__ params, const float* __restrict__ master, 
     for (long long i = (long long)blockIdx.x * OPT_THREADS + threadIdx.x; i < total; i += (long long)gridDim.x * OPT_THREADS) {
         const long long l = i / tv.n, idx = i - l * tv.n;
         params[tv.p_base + l * tv.p_stride + idx] =
-            stochastic_round_bf16(master[tv.o_base + l * tv.o_stride + idx], squirrel_noise5(sr_position(idx, (int)l), tv.seed));
+            stochastic_round_bf16(master[tv.o_base + l * tv.o_stride + idx], squirrel_noise5(sr_position(idx, (int)l + tv.pad), tv.seed));
     }
 }
 

@@ -108,6 +108,9 @@ def num_parameters(cfg):
 
 
 class GPT:
+    family = "gpt2"
+    norm_params = ("ln1w", "ln1b", "ln2w", "ln2b")      # per-layer tensors that the forward pass reads before the layer's first GEMM
+
     def __init__(self, cfg, device="cpu", dtype=None, recompute=1, flat_allocator=None):
         """``flat_allocator(kind, numel, dtype)`` (kind = 'params' | 'grads') may supply the two flat buffers, e.g. from
         symmetric memory that peer GPUs can address; by default they are ordinary tensors."""
@@ -141,7 +144,9 @@ class GPT:
         self.inputs = None
         self.targets = None
         self.mean_loss = None          # device scalar after a backward with targets
-        self.grad_hook = None          # called as grad_hook(layer or -1 for the embeddings/final LN) on the last micro-step
+        self.grad_hook = None
+        # set by a communication backend whose all-gather may still be in flight when forward starts (parallel/p2p.py)
+        self.param_sync = None          # called as grad_hook(layer or -1 for the embeddings/final LN) on the last micro-step
 
     # ------------------------------------------------------------------ parameters
     def _views(self, flat):
@@ -229,6 +234,9 @@ class GPT:
         if tokens.data_ptr() != self.inputs.data_ptr():
             self.inputs.copy_(tokens, non_blocking=True)
         nvtx = self.device.type == "cuda"
+        ps = self.param_sync
+        if ps is not None:
+            ps.wait(-1)
         ops.encoder_forward(a["encoded"], self.inputs, p["wte"], p["wpe"])
         ops.layernorm_forward(a["ln1"][0], a["ln1_mean"][0], a["ln1_rstd"][0], a["encoded"], p["ln1w"][0], p["ln1b"][0])
         for l in range(L):
@@ -236,7 +244,7 @@ class GPT:
             lln = 0 if self.recompute >= 2 else l
             lg = 0 if self.recompute >= 1 else l
             residual = a["encoded"] if l == 0 else a["residual3"][l - 1]
-            ops.matmul_forward(a["qkv"][l], a["ln1"][lln], p["qkvw"][l], p["qkvb"][l])
+            ops.matmul_forward(a["qkv"][l], a["ln1"][lln], p["qkvw"][l], p["qkvb"][l], ready=(ps.flags(l) if ps is not None else None))
             ops.attention_forward(a["atty"][l], a["lse"][l], a["qkv"][l], B, T, NH)
             ops.matmul_forward(a["scratch_btc"], a["atty"][l], p["attprojw"][l], p["attprojb"][l])
             ops.fused_residual_forward(a["residual2"][l], a["ln2"][lln], a["ln2_mean"][l], a["ln2_rstd"][l], residual,

@@ -131,6 +131,7 @@ def rope_table(cfg, length=None):
 
 class Llama:
     family = "llama3"
+    norm_params = ("ln1w", "ln2w")      # per-layer tensors that the forward pass reads before the layer's first GEMM
     decayed = DECAYED
 
     def __init__(self, cfg, device="cpu", dtype=None, recompute=1, flat_allocator=None):
@@ -168,6 +169,8 @@ class Llama:
         self.targets = None
         self.mean_loss = None
         self.grad_hook = None
+        # set by a communication backend whose all-gather may still be in flight when forward starts (parallel/p2p.py)
+        self.param_sync = None
         self.freqs = rope_table(cfg).to(self.device)
 
     # ------------------------------------------------------------------ parameters
@@ -259,6 +262,9 @@ class Llama:
         if tokens.data_ptr() != self.inputs.data_ptr():
             self.inputs.copy_(tokens, non_blocking=True)
         nvtx = self.device.type == "cuda"
+        ps = self.param_sync
+        if ps is not None:
+            ps.wait(-1)
         ops.encoder_forward(a["encoded"], self.inputs, p["wte"], None)
         ops.rmsnorm_forward(a["ln1"][0], a["ln1_rstd"][0], a["encoded"], p["ln1w"][0], eps)
         for l in range(L):
@@ -266,7 +272,7 @@ class Llama:
             lln = 0 if self.recompute >= 2 else l
             lg = 0 if self.recompute >= 1 else l
             residual = a["encoded"] if l == 0 else a["residual3"][l - 1]
-            ops.matmul_forward(a["qkv_raw"], a["ln1"][lln], p["qkvw"][l], None)
+            ops.matmul_forward(a["qkv_raw"], a["ln1"][lln], p["qkvw"][l], None, ready=(ps.flags(l) if ps is not None else None))
             ops.rope_forward(a["qkv"][l], a["qkv_raw"], self.freqs, T, NH, NKV)
             ops.attention_forward(a["atty"][l], a["lse"][l], a["qkv"][l], B, T, NH)
             ops.matmul_forward(a["scratch_btc"], a["atty"][l], p["attprojw"][l], None)

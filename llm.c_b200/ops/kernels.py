@@ -52,8 +52,10 @@ def sm_count(device):
     return _sm_count[idx]
 
 
-def gemm(a, b, d, M, N, K, lda, ldb, ldd, a_mn, b_mn, mode, bias=None, aux=None, accumulate=False, splits=1, max_ctas=0):
-    """Dispatches to the two-SM kernel (256 x 256 tiles on CTA pairs) for problems with enough tiles, else to the single-CTA one."""
+def gemm(a, b, d, M, N, K, lda, ldb, ldd, a_mn, b_mn, mode, bias=None, aux=None, accumulate=False, splits=1, max_ctas=0, ready=None):
+    """Dispatches to the two-SM kernel (256 x 256 tiles on CTA pairs) for problems with enough tiles, else to the single-CTA one.
+    ``ready`` (an object with flags_ptr, n, seq and wait()) marks the B operand as the target of an all-gather in flight: the
+    two-SM kernel polls the peers' flags itself before its first load; the single-CTA kernel runs after ``ready.wait()``."""
     global _launches
     lib = _lib.cuda()
     _launches += 1
@@ -71,9 +73,16 @@ def gemm(a, b, d, M, N, K, lda, ldb, ldd, a_mn, b_mn, mode, bias=None, aux=None,
             if splits > 1:
                 ws = _scratch.get("gemm_ws", wsf.value, torch.float32, d.device)
             cnt = _scratch.get("gemm2_cnt", nc.value, torch.int32, d.device, zero=True)
+        if ready is not None:
+            check(lib.llmc_gemm2_after_flags(_p(a), _p(b), _p(d), _p(bias), _p(aux), M, N, K, lda, ldb, ldd, int(a_mn), int(b_mn), mode,
+                                             int(accumulate), splits, _p(ws), _p(cnt), ctypes.c_void_p(ready.flags_ptr), ready.n, ready.seq,
+                                             _stream()), "llmc_gemm2_after_flags")
+            return
         check(lib.llmc_gemm2(_p(a), _p(b), _p(d), _p(bias), _p(aux), M, N, K, lda, ldb, ldd, int(a_mn), int(b_mn), mode, int(accumulate), splits,
                              _p(ws), _p(cnt), _stream()), "llmc_gemm2")
         return
+    if ready is not None:
+        ready.wait()
     if mode == MODE_ACCUM and splits > 1:
         wsf, nc = ctypes.c_longlong(0), ctypes.c_int(0)
         lib.llmc_gemm_workspace(M, N, splits, ctypes.byref(wsf), ctypes.byref(nc))
@@ -83,13 +92,13 @@ def gemm(a, b, d, M, N, K, lda, ldb, ldd, a_mn, b_mn, mode, bias=None, aux=None,
                         int(accumulate), splits, _p(ws), _p(cnt), max_ctas, _stream()), "llmc_gemm")
 
 
-def matmul_forward(out, inp, weight, bias=None, pre_gelu=None):
+def matmul_forward(out, inp, weight, bias=None, pre_gelu=None, ready=None):
     """out[M,OC] = inp[M,C] @ weight[OC,C]^T (+ bias).  With ``pre_gelu`` the pre-activation is stored there and
     ``out`` receives its tanh-GELU (reference: matmul_forward_cublaslt, llmc/matmul.cuh:230-242)."""
     M, C = inp.shape
     OC = weight.shape[0]
     mode = MODE_GELU if pre_gelu is not None else MODE_STORE
-    gemm(inp, weight, out, M, OC, C, C, C, OC, 0, 0, mode, bias=bias, aux=pre_gelu)
+    gemm(inp, weight, out, M, OC, C, C, C, OC, 0, 0, mode, bias=bias, aux=pre_gelu, ready=ready)
 
 
 def matmul_dgrad(dinp, dout, weight, pre_gelu=None):
@@ -279,13 +288,14 @@ def swiglu_backward(dx12, dh, x12):
 
 
 def make_table(views):
-    """views: list of dicts(p_base, p_stride, o_base, o_stride, n, L, wd, seed)."""
+    """views: list of dicts(p_base, p_stride, o_base, o_stride, n, L, wd, seed[, l_base])."""
     tab = TensorTable()
     assert len(views) <= 16
     for i, v in enumerate(views):
         t = tab.t[i]
         t.p_base, t.p_stride, t.o_base, t.o_stride = v["p_base"], v["p_stride"], v["o_base"], v["o_stride"]
         t.n, t.L, t.wd, t.seed = v["n"], v["L"], float(v.get("wd", 0.0)), int(v.get("seed", 0)) & 0xFFFFFFFF
+        t.pad = int(v.get("l_base", 0))        # layer index of the view's first slice (enters the stochastic-rounding noise index)
     tab.count = len(views)
     return tab
 

@@ -26,7 +26,9 @@ def gelu_grad(x):
     return 0.5 * (1.0 + t) + x * 0.5 * (1.0 - t * t) * GELU_K * (1.0 + 3.0 * 0.044715 * x * x)
 
 
-def matmul_forward(out, inp, weight, bias=None, pre_gelu=None):
+def matmul_forward(out, inp, weight, bias=None, pre_gelu=None, ready=None):
+    if ready is not None:
+        ready.wait()
     y = _f(inp) @ _f(weight).t()
     if bias is not None:
         y = y + _f(bias)

@@ -34,9 +34,11 @@ def _cfg_lib():
         lib.llmc_p2p_allreduce_scalar.restype = I
         lib.llmc_p2p_allreduce_scalar.argtypes = [P, P, I, I, U, P]
         lib.llmc_p2p_adamw_allgather.restype = I
-        lib.llmc_p2p_adamw_allgather.argtypes = [P, P, P, P, P, P, ctypes.POINTER(_lib.TensorTable), I, I, F, F, F, F, I, F, P, F, U, P, I, P]
+        lib.llmc_p2p_adamw_allgather.argtypes = [P, P, P, P, P, P, ctypes.POINTER(_lib.TensorTable), I, I, F, F, F, F, I, F, P, F, U, P, I, I, P]
         lib.llmc_p2p_wait.restype = I
-        lib.llmc_p2p_wait.argtypes = [P, I, I, I, U, P]
+        lib.llmc_p2p_wait.argtypes = [P, I, I, I, I, U, P]
+        lib.llmc_p2p_ag_flag_offset.restype = I
+        lib.llmc_p2p_ag_flag_offset.argtypes = [I]
         lib.llmc_p2p_barrier.restype = I
         lib.llmc_p2p_barrier.argtypes = [P, I, I, U, P]
         _configured = True
@@ -55,10 +57,13 @@ class SymmetricArena:
         self.symm = symm
         self.cfg = dist_cfg
         self.group = dist.group.WORLD
-        try:
-            symm.enable_symm_mem_for_group(self.group.group_name)
-        except Exception:
-            pass
+        import warnings
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")            # newer PyTorch enables every group by itself and only warns here
+            try:
+                symm.enable_symm_mem_for_group(self.group.group_name)
+            except Exception:
+                pass
 
     def alloc(self, numel, dtype, zero=True):
         t = self.symm.empty(int(numel), dtype=dtype, device=self.cfg.device)
@@ -67,6 +72,34 @@ class SymmetricArena:
         handle = self.symm.rendezvous(t, self.group.group_name)
         ptrs = [int(p) for p in handle.buffer_ptrs]
         return t, ptrs, handle
+
+
+class _Ready:
+    """What a GEMM needs to wait for a parameter group inside the kernel: address of the N flags, N, the sequence number."""
+
+    def __init__(self, backend, channel):
+        self.backend, self.channel = backend, channel
+        self.flags_ptr, self.n, self.seq = backend.flag_address(channel), backend.N, backend.published_seq
+
+    def wait(self):
+        self.backend.wait_params(self.channel)
+
+
+class ParamSync:
+    """The forward pass's view of parameters that may still be arriving from the other ranks.  ``wait(-1)`` precedes the first
+    read of the shared group (embeddings, norms, LM head); ``flags(l)`` goes to the first GEMM of layer l, which polls inside
+    the kernel."""
+
+    def __init__(self, backend):
+        self.backend = backend
+
+    def wait(self, layer):
+        self.backend.wait_params(layer + 1)
+
+    def flags(self, layer):
+        if self.backend.published_seq == 0:
+            return None
+        return _Ready(self.backend, layer + 1)
 
 
 class P2PBackend:
@@ -92,6 +125,8 @@ class P2PBackend:
         self.scalar_seq = 0
         self.barrier_seq = 0
         self.reduced_this_step = False
+        self.published_seq = 0  # sequence number of the last parameter publication (0: parameters are local, nothing to wait for)
+        model.param_sync = ParamSync(self)
         torch.cuda.synchronize()
         dist.barrier()          # every rank's buffers are zeroed and mapped before any kernel touches a peer
 
@@ -134,17 +169,51 @@ class P2PBackend:
                                                  ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)), "llmc_p2p_allreduce_scalar")
         return t
 
+    # ---- parameter groups of the fused update + all-gather, in the order the forward pass consumes them:
+    #      group 0 = everything the forward pass touches before / outside the layer GEMMs (embeddings, final norm, LM head and the
+    #      small per-layer norm parameters), group 1 + l = the matrices and biases of layer l.
+    def _groups(self, views):
+        L = self.model.cfg.num_layers
+        early = getattr(self.model, "norm_params", ())
+        shared, layers = [], [[] for _ in range(L)]
+        for v in views:
+            if v["L"] == 1 or v["name"] in early:
+                shared.append(v)
+            else:
+                for l in range(v["L"]):
+                    w = dict(v)
+                    w.update(p_base=v["p_base"] + l * v["p_stride"], o_base=v["o_base"] + l * v["o_stride"], L=1, l_base=l)
+                    layers[l].append(w)
+        return [shared] + layers
+
     def adamw_allgather(self, master, m, v, views, lr, beta1, beta2, eps, t, grad_scale, norm_sq, grad_clip):
-        tab = kernels.make_table(views)
-        kernels._launches += 2
+        """AdamW on the own shards and peer stores of the rounded parameters, one launch per parameter group; each launch raises
+        the group's flags on every peer when its stores are out.  Nothing waits here: the consumers do (``ParamSync``)."""
         st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-        check(self.lib.llmc_p2p_adamw_allgather(self.c_params, self.c_sig, kernels._p(master), kernels._p(self.grads_t), kernels._p(m),
-                                                kernels._p(v), ctypes.byref(tab), self.r, self.N, lr, beta1, beta2, eps, int(t), grad_scale,
-                                                kernels._p(norm_sq), grad_clip, self.seq, kernels._p(self.done_counter), 4 * self.ctas, st),
-              "llmc_p2p_adamw_allgather")
-        # the next consumer of the parameters (the following forward) runs after every peer has published its shards
-        check(self.lib.llmc_p2p_wait(self.c_sig, self.r, self.N, 0, self.seq, st), "llmc_p2p_wait")
+        for ch, group in enumerate(self._groups(views)):
+            if not group:
+                continue
+            tab = kernels.make_table(group)
+            kernels._launches += 1
+            check(self.lib.llmc_p2p_adamw_allgather(self.c_params, self.c_sig, kernels._p(master), kernels._p(self.grads_t), kernels._p(m),
+                                                    kernels._p(v), ctypes.byref(tab), self.r, self.N, lr, beta1, beta2, eps, int(t), grad_scale,
+                                                    kernels._p(norm_sq), grad_clip, self.seq, kernels._p(self.done_counter), 4 * self.ctas, ch,
+                                                    st), "llmc_p2p_adamw_allgather")
+        self.published_seq = self.seq
         self.reduced_this_step = False
+
+    def wait_params(self, channel=None):
+        """Tiny wait kernel(s) on the current stream: all groups, or one (0 = shared group, 1 + l = layer l)."""
+        if self.published_seq == 0:
+            return
+        st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        chans = range(self.model.cfg.num_layers + 1) if channel is None else [channel]
+        for ch in chans:
+            kernels._launches += 1
+            check(self.lib.llmc_p2p_wait(self.c_sig, self.r, self.N, 0, ch, self.published_seq, st), "llmc_p2p_wait")
+
+    def flag_address(self, channel):
+        return self.sig_ptrs[self.r] + 8 * self.lib.llmc_p2p_ag_flag_offset(channel)
 
     def all_gather_slices(self, params_flat, slices):
         raise RuntimeError("the P2P backend gathers inside adamw_allgather")

@@ -199,6 +199,12 @@ class ShardedAdamW:
         if self.sharded:
             self.backend.all_gather_slices(model.params_flat, self._all_slices())
 
+    def sync_params(self):
+        """Blocks the current stream until this rank's copy of the parameters is complete.  The forward pass does its own,
+        finer-grained waiting; anything else that reads ``params_flat`` after a step (checkpoint writer, export) calls this."""
+        if hasattr(self.backend, "wait_params"):
+            self.backend.wait_params()
+
     def _all_slices(self):
         slices = []
         for name, off, per, L in self.model.tensor_sizes():

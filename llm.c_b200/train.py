@@ -296,6 +296,7 @@ class Trainer:
         c, d = self.cfg, self.dist
         model_path, state_path, done_path = checkpoint.checkpoint_paths(c.output_log_dir, step, d.process_rank)
         self.print0("Writing model to %s" % model_path)
+        self.opt.sync_params()                      # every rank's shards of the last update have landed in this rank's copy
         if d.is_main:
             checkpoint.write_model(model_path, self.model)
         checkpoint.write_state(state_path, num_processes=d.num_processes, process_rank=d.process_rank, use_master_weights=self.opt.use_master,
@@ -350,6 +351,7 @@ class Trainer:
         if self._sample_model is None:
             # a second model object over the same parameter buffer, with its own (small) activation set
             sm = type(m)(m.cfg, self.device, m.dtype, recompute=2, flat_allocator=lambda kind, numel, dt: m.params_flat)
+            sm.param_sync = m.param_sync
             self._sample_model = sm
         sm = self._sample_model
         eot = min(self.tokenizer.eot_token, m.cfg.vocab_size - 1)

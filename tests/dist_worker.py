@@ -72,6 +72,7 @@ def main():
         from llmc_b200 import _lib
         status = _lib.read_status()
         assert status == 0, "kernel status 0x%08x on rank %d" % (status, rank)
+    opt.sync_params()
     if rank == 0:
         torch.save({"params": model.params_flat.float().cpu(), "losses": losses, "backend": opt.backend.name, "zero": opt.zero_stage}, a.out)
     pdist.barrier(d)

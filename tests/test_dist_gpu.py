@@ -12,8 +12,9 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 WORKER = os.path.join(HERE, "dist_worker.py")
 
 
-def launch(world, out, extra, port, timeout=600):
+def launch(world, out, extra, port, timeout=600, env_extra=None):
     env = dict(os.environ)
+    env.update(env_extra or {})
     if world == 1:
         cmd = [sys.executable, WORKER, "--out", out] + extra
     else:
@@ -32,7 +33,16 @@ def test_p2p_and_nccl_zero1_match_single_gpu(tmp_path):
     assert r.returncode == 0, r.stdout[-3000:]
     r = launch(world, p2p, ["--device", "cuda", "--zero", "1", "--slots", str(world), "--backend", "p2p"], 29542)
     assert r.returncode == 0, r.stdout[-3000:]
+    # the same run with every GEMM on the two-SM kernel: the first GEMM of each layer then polls the all-gather flags inside the kernel
+    p2p_fused = str(tmp_path / "p2p_fused.pt")
+    r = launch(world, p2p_fused, ["--device", "cuda", "--zero", "1", "--slots", str(world), "--backend", "p2p"], 29543,
+               env_extra={"LLMC_GEMM_2SM_MIN_TILES": "1"})
+    assert r.returncode == 0, r.stdout[-3000:]
+    pf = torch.load(p2p_fused)
     s, n, p = torch.load(single), torch.load(nccl), torch.load(p2p)
+    assert pf["backend"] == "p2p"
+    assert max(abs(x - y) for x, y in zip(p["losses"], pf["losses"])) < 2e-2
+    assert (p["params"] - pf["params"]).abs().max().item() < 2e-2
     assert p["backend"] == "p2p" and n["backend"] == "nccl" and p["zero"] == 1
     for other in (n, p):
         assert max(abs(x - y) for x, y in zip(s["losses"], other["losses"])) < 3e-2, (s["losses"], other["losses"])
