@@ -34,6 +34,11 @@ PUBLISHED_BASELINE = 1.75e6     # tok/s, 8 x A100 80GB, reference scripts/run_gp
 MODELS = {"d12": "gpt2_124M", "d24": "gpt2_350M", "d36": "gpt2_774M", "d48": "gpt2_1558M"}
 
 
+def metric_name(model):
+    """The headline metric is named for the model it was measured on (the published baseline number exists for d12 only)."""
+    return METRIC if model == "d12" else "%s_train_tokens_per_sec" % MODELS.get(model, model)
+
+
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -57,8 +62,38 @@ class ClockSampler:
 
     def __init__(self, index):
         self.index, self.proc, self.lines = index, None, []
+        self.nvml_samples, self.nvml_stop, self.thread = None, None, None
+
+    def _nvml_loop(self, pynvml, handle):
+        names = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
+        reasons_fn = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
+        while not self.nvml_stop.is_set():
+            try:
+                mask = reasons_fn(handle)
+                self.nvml_samples.append((float(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)),
+                                          float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM)),
+                                          pynvml.nvmlDeviceGetPowerUsage(handle) / 1000.0, [n for bit, n in names.items() if mask & bit]))
+            except Exception:
+                pass
+            time.sleep(0.025)
 
     def start(self):
+        # NVML in-process (read-only queries every 25 ms: short multi-GPU steps still get a few samples); nvidia-smi otherwise
+        try:
+            import pynvml
+            import torch
+            pynvml.nvmlInit()
+            try:
+                uuid = str(torch.cuda.get_device_properties(self.index).uuid)
+                handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid) if not uuid.startswith("GPU-") else uuid)
+            except Exception:
+                handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.nvml_samples, self.nvml_stop = [], threading.Event()
+            self.thread = threading.Thread(target=self._nvml_loop, args=(pynvml, handle), daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.nvml_samples = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits",
                                           "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
@@ -72,6 +107,14 @@ class ClockSampler:
             self.lines.append(line.strip())
 
     def stop(self):
+        if self.nvml_samples is not None:
+            self.nvml_stop.set()
+            self.thread.join(timeout=2)
+            smp = self.nvml_samples
+            if not smp:
+                return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+            return {"sm_mhz": statistics.median(x[0] for x in smp), "sm_max_mhz": max(x[1] for x in smp),
+                    "power_w_max": max(x[2] for x in smp), "samples": len(smp), "reasons": sorted({r for x in smp for r in x[3]})}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -203,8 +246,8 @@ def run_ours(a):
     flops_tok = model.flops_per_token(a.seq)
     if rank == 0:
         out = {
-            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
-            "ms_per_step": dev_ms / a.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": value / PUBLISHED_BASELINE,
+            "metric": metric_name(a.model), "value": value, "unit": "tokens/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
+            "ms_per_step": dev_ms / a.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": (value / PUBLISHED_BASELINE if a.model == "d12" else None),
             "dtype": "bf16", "data": "synthetic (seeded uniform-random uint16 tokens, random-init weights)",
             "config": {"model": MODELS.get(a.model, a.model), "global_batch": a.total_batch, "micro_batch_per_gpu": a.batch, "seq_len": a.seq,
                        "grad_accum_steps": G, "parallelism": ("dp%d-zero%d" % (world, opt.zero_stage)) if world > 1 else "single",
@@ -290,8 +333,8 @@ def run_reference(a):
     ms_per_step = sum(timed) / len(timed)
     value = a.total_batch / (ms_per_step / 1000.0)
     out = {
-        "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms_per_step,
-        "higher_is_better": True, "scaling": "strong", "vs_baseline": value / PUBLISHED_BASELINE, "dtype": "bf16",
+        "metric": metric_name(a.model), "value": value, "unit": "tokens/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms_per_step,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": (value / PUBLISHED_BASELINE if a.model == "d12" else None), "dtype": "bf16",
         "data": "synthetic (seeded uniform-random uint16 tokens, random-init weights)",
         "config": {"model": MODELS.get(a.model, a.model), "global_batch": a.total_batch, "micro_batch_per_gpu": a.batch, "seq_len": a.seq,
                    "parallelism": ("dp%d-zero%d" % (world, a.zero)) if world > 1 else "single", "recompute": a.recompute,
