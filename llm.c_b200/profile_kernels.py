@@ -100,11 +100,41 @@ def case(op):
         x = _bf(65536 * 3072)
         out = torch.empty_like(x)
         return (lambda: K.gelu_forward(out, x)), 4.0 * x.numel(), 0.0
+    if op in ("rms_fwd", "rms_fused_residual", "rms_bwd"):
+        N, Cw = 16384, 4096
+        x, y, w, dy = _bf(N, Cw), _bf(N, Cw), _bf(Cw) + 1, _bf(N, Cw)
+        out, res, dx, dw = torch.empty_like(x), torch.empty_like(x), _bf(N, Cw), _bf(Cw)
+        rstd = torch.empty(N, device=DEV)
+        K.rmsnorm_forward(out, rstd, x, w, 1e-5)
+        fns = {
+            "rms_fwd": (lambda: K.rmsnorm_forward(out, rstd, x, w, 1e-5), 2.0 * 2 * N * Cw),
+            "rms_fused_residual": (lambda: K.rmsnorm_fused_residual_forward(res, out, rstd, x, y, w, 1e-5), 2.0 * 4 * N * Cw),
+            "rms_bwd": (lambda: K.rmsnorm_backward(dx, dw, dy, x, w, rstd, True, True), 2.0 * 4 * N * Cw),
+        }
+        fn, bytes_ = fns[op]
+        return fn, bytes_, 0.0
+    if op in ("rope_fwd", "rope_bwd"):
+        from .models import llama3
+        B, T, NH, NKV, HS = 4, 4096, 32, 8, 128
+        cfg = llama3.LlamaConfig(max_seq_len=T, num_heads=NH, num_kv_heads=NKV, channels=NH * HS)
+        freqs = llama3.rope_table(cfg).to(DEV)
+        raw, packed = _bf(B * T, (NH + 2 * NKV) * HS), _bf(B * T, 3 * NH * HS)
+        nbytes = 2.0 * (raw.numel() + packed.numel())
+        if op == "rope_fwd":
+            return (lambda: K.rope_forward(packed, raw, freqs, T, NH, NKV)), nbytes, 0.0
+        return (lambda: K.rope_backward(raw, packed, freqs, T, NH, NKV)), nbytes, 0.0
+    if op in ("swiglu_fwd", "swiglu_bwd"):
+        N, H = 16384, 14336
+        x12, h, dh, dx12 = _bf(N, 2 * H), _bf(N, H), _bf(N, H), torch.empty(N, 2 * H, device=DEV, dtype=torch.bfloat16)
+        if op == "swiglu_fwd":
+            return (lambda: K.swiglu_forward(h, x12)), 2.0 * 3 * N * H, 0.0
+        return (lambda: K.swiglu_backward(dx12, dh, x12)), 2.0 * 5 * N * H, 0.0
     raise SystemExit("unknown operator %r" % op)
 
 
 OPS = ["gemm_fwd", "gemm_gelu", "gemm_dgrad", "gemm_dgelu", "gemm_wgrad", "attn_fwd", "attn_bwd", "ln_fwd", "fused_residual", "ln_bwd", "ln_bwd_colsum",
-       "classifier", "encoder_fwd", "encoder_bwd", "adamw", "norm", "bias_grad", "gelu"]
+       "classifier", "encoder_fwd", "encoder_bwd", "adamw", "norm", "bias_grad", "gelu", "rms_fwd", "rms_fused_residual", "rms_bwd", "rope_fwd",
+       "rope_bwd", "swiglu_fwd", "swiglu_bwd"]
 
 
 def main(argv):
