@@ -60,6 +60,7 @@ def cuda():
         "llmc_encoder_bwd": (I, [P, P, P, P, I, I, I, I, I, I, U, S]),
         "llmc_fused_classifier": (I, [P, P, P, F, I, I, I, I, I, S]),
         "llmc_gelu_fwd": (I, [P, P, L, S]),
+        "llmc_gemm_tf32": (I, [P, P, P, P, I, I, I, I, I, I, I, S]),
         "llmc_rmsnorm_fwd": (I, [P, P, P, P, I, I, F, S]),
         "llmc_rmsnorm_fused_residual_fwd": (I, [P, P, P, P, P, P, I, I, F, S]),
         "llmc_rmsnorm_bwd_scratch": (L, [I, I]),

@@ -118,6 +118,23 @@ def matmul_wgrad(dweight, dout, inp, accumulate=True):
     gemm(dout, inp, dweight, OC, C, M, OC, C, C, 1, 1, MODE_ACCUM, accumulate=accumulate, splits=splits)
 
 
+def gemm_tf32(d, a, b, bias=None, accumulate=False):
+    """d[M,N] (+)= a[M,K] @ b[N,K]^T (+ bias): fp32 tensors, tcgen05 kind::tf32 with fp32 accumulation (the matmul of the
+    full-precision mode; the reference runs cuBLAS in TF32 there when -f 1, train_gpt2_fp32.cu / PRECISION=FP32)."""
+    global _launches
+    M, K = a.shape
+    N = b.shape[0]
+    assert a.dtype == b.dtype == d.dtype == torch.float32 and b.shape[1] == K and tuple(d.shape) == (M, N)
+    assert a.stride(1) == 1 and b.stride(1) == 1 and d.stride(1) == 1
+    _launches += 1
+    check(_lib.cuda().llmc_gemm_tf32(_p(a), _p(b), _p(d), _p(bias), M, N, K, a.stride(0), b.stride(0), d.stride(0), int(accumulate), _stream()),
+          "llmc_gemm_tf32")
+
+
+def tf32_shapes_ok(*dims):
+    return all(int(x) % 4 == 0 for x in dims)
+
+
 def bias_grad(dbias, dout, accumulate=True):
     """dbias[OC] (+)= column sums of dout[M,OC]."""
     global _launches

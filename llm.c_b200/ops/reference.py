@@ -26,9 +26,24 @@ def gelu_grad(x):
     return 0.5 * (1.0 + t) + x * 0.5 * (1.0 - t * t) * GELU_K * (1.0 + 3.0 * 0.044715 * x * x)
 
 
+def _tf32_kernel(*tensors):
+    """True if the product should run on this library's TF32 tensor-core kernel: fp32 tensors on a CUDA device with TF32 allowed
+    (the -f switch of the trainer).  Otherwise the product is PyTorch's."""
+    t0 = tensors[0]
+    return (t0.is_cuda and torch.backends.cuda.matmul.allow_tf32 and all(t.dtype == torch.float32 and t.dim() == 2 for t in tensors)
+            and all(x % 4 == 0 for t in tensors for x in t.shape))
+
+
 def matmul_forward(out, inp, weight, bias=None, pre_gelu=None, ready=None):
     if ready is not None:
         ready.wait()
+    if _tf32_kernel(out, inp, weight):
+        from . import kernels
+        dst = pre_gelu if pre_gelu is not None else out
+        kernels.gemm_tf32(dst, inp, weight, bias)
+        if pre_gelu is not None:
+            out.copy_(gelu(pre_gelu))
+        return
     y = _f(inp) @ _f(weight).t()
     if bias is not None:
         y = y + _f(bias)
@@ -39,6 +54,12 @@ def matmul_forward(out, inp, weight, bias=None, pre_gelu=None, ready=None):
 
 
 def matmul_dgrad(dinp, dout, weight, pre_gelu=None):
+    if _tf32_kernel(dinp, dout, weight):
+        from . import kernels
+        kernels.gemm_tf32(dinp, dout, weight.t().contiguous())        # the kernel wants both operands K-major
+        if pre_gelu is not None:
+            dinp.mul_(gelu_grad(pre_gelu))
+        return
     y = _f(dout) @ _f(weight)
     if pre_gelu is not None:
         y = y * gelu_grad(_f(pre_gelu))
@@ -46,6 +67,10 @@ def matmul_dgrad(dinp, dout, weight, pre_gelu=None):
 
 
 def matmul_wgrad(dweight, dout, inp, accumulate=True):
+    if _tf32_kernel(dweight, dout, inp):
+        from . import kernels
+        kernels.gemm_tf32(dweight, dout.t().contiguous(), inp.t().contiguous(), None, accumulate)
+        return
     y = _f(dout).t() @ _f(inp)
     if accumulate:
         y = y + _f(dweight)

@@ -320,3 +320,28 @@ def test_two_sm_gemm_forward_and_dgrad(M, N, K, monkeypatch):
     KN.matmul_dgrad(dinp, dout.to(DEV), w.to(DEV), pre_gelu=pg.to(DEV))
     R.matmul_dgrad(rd, dout, w, pre_gelu=pg)
     close(dinp, rd, 3e-2, 1e-2, "2sm dgrad+dgelu")
+
+
+@pytest.mark.parametrize("M,N,K,acc,use_bias", [(128, 128, 32, False, False), (256, 384, 768, False, True), (200, 132, 100, True, False),
+                                                (1024, 768, 3072, True, True), (64, 50304 // 8, 768, False, False)])
+def test_gemm_tf32(M, N, K, acc, use_bias):
+    """The full-precision mode's matmul: fp32 in memory, TF32 products (10-bit mantissa inputs), fp32 accumulation."""
+    g = torch.Generator().manual_seed(M + N + K)
+    a = torch.randn(M, K, generator=g)
+    b = torch.randn(N, K, generator=g) * 0.05
+    bias = torch.randn(N, generator=g) if use_bias else None
+    d0 = torch.randn(M, N, generator=g)
+    buf = torch.full((M + 4, N), 7.0, device=DEV)
+    buf[:M].copy_(d0)
+    KN.gemm_tf32(buf[:M], a.to(DEV), b.to(DEV), None if bias is None else bias.to(DEV), accumulate=acc)
+    ref = a.double() @ b.double().t()
+    if bias is not None:
+        ref = ref + bias.double()
+    if acc:
+        ref = ref + d0.double()
+    # TF32 keeps 10 mantissa bits of each input (truncated, not rounded): per-product relative error up to 2^-9, summed over K
+    # terms of magnitude ~ |a| |b| = 0.05; the factor covers the tail of the maximum over all outputs
+    tol = 2.0 ** -9 * math.sqrt(K) * 0.05 * 4.0 + 1e-5
+    err = (buf[:M].double().cpu() - ref).abs().max().item()
+    assert err < tol, "max err %g (tolerance %g)" % (err, tol)
+    assert (buf[M:] == 7.0).all()

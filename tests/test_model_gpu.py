@@ -106,3 +106,25 @@ def test_fp32_mode_on_the_gpu_matches_the_cpu_path():
     opt.grad_norm_sq()
     opt.step(1e-3, 0.1, 1)
     assert not torch.equal(before, gm.params_flat) and torch.isfinite(gm.params_flat).all()
+
+
+def test_fp32_mode_with_tf32_kernel_tracks_the_cpu_path():
+    """With TF32 allowed the matmuls of the full-precision mode run on this library's kind::tf32 kernel."""
+    torch.backends.cuda.matmul.allow_tf32 = True
+    try:
+        gm = make("cuda", torch.float32, 0)
+        cm = make("cpu", torch.float32, 0)
+        x, y = batch(gm.cfg, 2, 64)
+        from llmc_b200.ops import kernels as KN
+        before = KN.launch_count()
+        for m, dev in ((gm, "cuda"), (cm, "cpu")):
+            m.forward(x.to(dev), y.to(dev))
+            m.backward()
+        assert KN.launch_count() - before >= 3 * (4 * gm.cfg.num_layers + 1)      # every matmul went through llmc_gemm_tf32
+        assert abs(float(gm.loss()) - float(cm.loss())) < 5e-3
+        for name in gpt2.PARAM_NAMES:
+            got, want = gm.grads[name].cpu(), cm.grads[name]
+            scale = want.abs().max().item() + 1e-6
+            assert (got - want).abs().max().item() < 0.02 * scale + 1e-5, name
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = False
