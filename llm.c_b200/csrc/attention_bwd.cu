@@ -30,7 +30,7 @@ namespace {
 constexpr int BT = 128;                             // tile rows (queries and keys)
 constexpr int CHUNK_BYTES = 128 * 64 * 2;           // 16 KB: 128 rows x 64 channels, one 128-byte-swizzled TMA box
 constexpr int PS_BYTES = BT * BT * 2;               // 32 KB
-constexpr int BWD_THREADS = 576;                    // TMA warp + MMA warp + 16 softmax warps
+constexpr int BWD_THREADS = 608;                    // TMA warp + score-product issuer + 16 softmax warps + accumulate-product issuer
 constexpr int BWD_TMEM_COLS = 512;
 
 // NC = number of 64-channel chunks of the (zero-padded) head: 1 -> head size 64, 2 -> head sizes 72..128.
@@ -185,63 +185,59 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
             }
         }
     } else if (warp == 1) {
+        // ---- issuer of the score products S = Q K^T and dP = dO V^T.  Tile g + 1 is issued as soon as the softmax threads hold
+        //      tile g in registers, so it runs underneath their exponentials.
         if (lane == 0) {
             constexpr uint32_t idesc_s = umma_idesc_bf16(BT, BT, 0, 0);
-            constexpr uint32_t idesc_acc = DKV ? umma_idesc_bf16(BT, HSP, 1, 1) : umma_idesc_bf16(BT, HSP, 0, 1);
-            // S = Q K^T and dP = dO V^T of streamed tile t (stage t & 1) against resident buffer rb
-            auto issue_sdp = [&](int st, int rb, bool last_of_item) {
-                const uint32_t xs = smem_u32(sStr + st * PAIR_BYTES), rs = smem_u32(sRes + rb * PAIR_BYTES);
-                const uint32_t q = DKV ? xs : rs, dO = (DKV ? xs : rs) + TILE_BYTES;
-                const uint32_t k = DKV ? rs : xs, v = (DKV ? rs : xs) + TILE_BYTES;
-                #pragma unroll
-                for (int kk = 0; kk < HSP / 16; kk++) {      // 64-channel chunks are 16 KB apart, 16 channels = 32 bytes inside a chunk
-                    const uint32_t off = (kk >> 2) * CHUNK_BYTES + (kk & 3) * 32;
-                    umma_ss(tS, umma_desc_sw128(q + off, 16, 1024), umma_desc_sw128(k + off, 16, 1024), idesc_s, kk > 0);
-                }
-                #pragma unroll
-                for (int kk = 0; kk < HSP / 16; kk++) {
-                    const uint32_t off = (kk >> 2) * CHUNK_BYTES + (kk & 3) * 32;
-                    umma_ss(tdP, umma_desc_sw128(dO + off, 16, 1024), umma_desc_sw128(v + off, 16, 1024), idesc_s, kk > 0);
-                }
-                umma_commit(sdp_full);
-                if (last_of_item) umma_commit(&res_empty[rb]);     // the resident pair is only read by these two products
-            };
             uint32_t t = 0;
-            int cst = 0; uint32_t cph = 0;                    // stream ring position of tile t
+            int st = 0; uint32_t ph = 0;                      // stream ring position of tile t
             int it = 0;
             bool ok = true;
-            if ((int)blockIdx.x < total) {
-                int fixed, b, h, cnt; decode(blockIdx.x, fixed, b, h, cnt);
-                ok = mbar_wait(&res_full[0], 0, abort_flag, a.status, 0x610) && mbar_wait(&x_full[0], 0, abort_flag, a.status, 0x611);
-                tc_fence_after();
-                if (ok) issue_sdp(0, 0, cnt == 1);
+            for (int w = blockIdx.x; w < total && ok; w += gridDim.x, it++) {
+                int fixed, b, h, cnt; decode(w, fixed, b, h, cnt);
+                const int rb = it % RB;
+                ok = mbar_wait(&res_full[rb], (it / RB) & 1, abort_flag, a.status, 0x610);
+                for (int n = 0; n < cnt && ok; n++, t++) {
+                    ok = ok && mbar_wait(&x_full[st], ph, abort_flag, a.status, 0x612);
+                    if (t > 0) ok = ok && mbar_wait(sdp_empty, (t - 1) & 1, abort_flag, a.status, 0x613);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t xs = smem_u32(sStr + st * PAIR_BYTES), rs = smem_u32(sRes + rb * PAIR_BYTES);
+                    const uint32_t q = DKV ? xs : rs, dO = (DKV ? xs : rs) + TILE_BYTES;
+                    const uint32_t k = DKV ? rs : xs, v = (DKV ? rs : xs) + TILE_BYTES;
+                    #pragma unroll
+                    for (int kk = 0; kk < HSP / 16; kk++) {      // 64-channel chunks are 16 KB apart, 16 channels = 32 bytes inside a chunk
+                        const uint32_t off = (kk >> 2) * CHUNK_BYTES + (kk & 3) * 32;
+                        umma_ss(tS, umma_desc_sw128(q + off, 16, 1024), umma_desc_sw128(k + off, 16, 1024), idesc_s, kk > 0);
+                    }
+                    #pragma unroll
+                    for (int kk = 0; kk < HSP / 16; kk++) {
+                        const uint32_t off = (kk >> 2) * CHUNK_BYTES + (kk & 3) * 32;
+                        umma_ss(tdP, umma_desc_sw128(dO + off, 16, 1024), umma_desc_sw128(v + off, 16, 1024), idesc_s, kk > 0);
+                    }
+                    umma_commit(sdp_full);
+                    if (n == cnt - 1) umma_commit(&res_empty[rb]);     // the resident pair is only read by these two products
+                    if (++st == XSTAGES) { st = 0; ph ^= 1; }
+                }
             }
+        }
+    } else if (warp == BWD_THREADS / 32 - 1) {
+        // ---- issuer of the accumulating products (dV += P^T dO, dK += dS^T Q, or dQ += dS K).  A second issuing thread: a
+        //      tcgen05.mma costs its issuer about a hundred cycles whatever its shape, and the two streams of products depend on
+        //      different events, so two threads keep the tensor pipe fed where one could not.
+        if (lane == 0) {
+            constexpr uint32_t idesc_acc = DKV ? umma_idesc_bf16(BT, HSP, 1, 1) : umma_idesc_bf16(BT, HSP, 0, 1);
+            uint32_t t = 0;
+            int cst = 0;
+            int it = 0;
+            bool ok = true;
             for (int w = blockIdx.x; w < total && ok; w += gridDim.x, it++) {
                 int fixed, b, h, cnt; decode(w, fixed, b, h, cnt);
                 const int ab = it % ACCBUF;
                 const uint32_t acc0 = tAcc + ab * (2 * HSP), acc1 = acc0 + HSP;
+                ok = mbar_wait(&acc_empty[ab], ((it / ACCBUF) & 1) ^ 1, abort_flag, a.status, 0x616);
                 for (int n = 0; n < cnt && ok; n++, t++) {
-                    // S / dP of the next tile (possibly of the next work item) as soon as the softmax threads hold tile t in registers
-                    auto lookahead = [&]() {
-                        bool have_next = true, next_new_item = false; int ncnt = cnt, nn = n + 1;
-                        if (nn == cnt) {
-                            if (w + (int)gridDim.x < total) { int f2, b2, h2; decode(w + gridDim.x, f2, b2, h2, ncnt); nn = 0; next_new_item = true; }
-                            else have_next = false;
-                        }
-                        if (!have_next) return;
-                        const int nit = it + (next_new_item ? 1 : 0);
-                        if (next_new_item) ok = ok && mbar_wait(&res_full[nit % RB], (nit / RB) & 1, abort_flag, a.status, 0x615);
-                        int nst = cst + 1; uint32_t nph = cph;
-                        if (nst == XSTAGES) { nst = 0; nph ^= 1; }
-                        ok = ok && mbar_wait(&x_full[nst], nph, abort_flag, a.status, 0x612);
-                        ok = ok && mbar_wait(sdp_empty, t & 1, abort_flag, a.status, 0x613);
-                        if (!ok) return;
-                        tc_fence_after();
-                        issue_sdp(nst, nit % RB, nn == ncnt - 1);
-                    };
-                    if (XSTAGES > 1) { lookahead(); if (!ok) break; }
-                    if (n == 0) ok = ok && mbar_wait(&acc_empty[ab], ((it / ACCBUF) & 1) ^ 1, abort_flag, a.status, 0x616);
-                    ok = ok && mbar_wait(pds_full, t & 1, abort_flag, a.status, 0x614);
+                    ok = mbar_wait(pds_full, t & 1, abort_flag, a.status, 0x614);
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t xs = smem_u32(sStr + cst * PAIR_BYTES);
@@ -267,9 +263,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
                     umma_commit(&x_empty[cst]);
                     umma_commit(pds_empty);
                     if (n == cnt - 1) umma_commit(&acc_full[ab]);
-                    // with a single stream stage the next tile can only be loaded once these MMAs have released it
-                    if (XSTAGES == 1) { lookahead(); if (!ok) break; }
-                    if (++cst == XSTAGES) { cst = 0; cph ^= 1; }
+                    if (++cst == XSTAGES) cst = 0;
                 }
             }
         }
