@@ -10,7 +10,7 @@ import torch
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 
-from llmc_b200.models import gpt2  # noqa: E402
+from llmc_b200.models import gpt2, llama3  # noqa: E402
 from llmc_b200.parallel import dist as pdist  # noqa: E402
 from llmc_b200.parallel.zero import ShardedAdamW  # noqa: E402
 
@@ -29,6 +29,7 @@ def main():
     ap.add_argument("--steps", type=int, default=4)
     ap.add_argument("--slots", type=int, default=2)    # data-parallel slots per optimizer step (= world size of the parallel run)
     ap.add_argument("--out", required=True)
+    ap.add_argument("--family", default="gpt2")        # gpt2 | llama3
     ap.add_argument("--fail-rank", type=int, default=-1)   # this rank raises before its second step (failure-detection test)
     a = ap.parse_args()
 
@@ -45,7 +46,11 @@ def main():
         def allocator(kind, numel, dt):
             bufs[kind] = arena.alloc(numel, dt)
             return bufs[kind][0]
-    model = gpt2.GPT(cfg, d.device, dtype, recompute=0, flat_allocator=allocator)
+    if a.family == "llama3":
+        cfg = llama3.config_from_descriptor("llama3:l=2,c=128,h=2,kv=1,t=64,v=512,m=64,f=1.0")
+        model = llama3.Llama(cfg, d.device, dtype, recompute=0, flat_allocator=allocator)
+    else:
+        model = gpt2.GPT(cfg, d.device, dtype, recompute=0, flat_allocator=allocator)
     model.init_random(42)
     model.allocate_grads()
     backend = None

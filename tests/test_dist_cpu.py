@@ -40,6 +40,19 @@ def test_two_ranks_match_single_process(tmp_path, zero):
     assert a["losses"][-1] < a["losses"][0]
 
 
+def test_llama_two_ranks_zero1_match_single_process(tmp_path):
+    single, multi = str(tmp_path / "single.pt"), str(tmp_path / "multi.pt")
+    r1 = launch(1, single, ["--device", "cpu", "--zero", "0", "--slots", "2", "--family", "llama3"], 0)
+    assert r1.returncode == 0, r1.stdout[-2000:]
+    r2 = launch(2, multi, ["--device", "cpu", "--zero", "1", "--slots", "2", "--family", "llama3"], 29521)
+    assert r2.returncode == 0, r2.stdout[-2000:]
+    a, b = torch.load(single), torch.load(multi)
+    assert b["zero"] == 1
+    assert max(abs(x - y) for x, y in zip(a["losses"], b["losses"])) < 1e-4
+    diff = (a["params"] - b["params"]).abs()
+    assert (diff > 1e-4).float().mean().item() < 1e-3 and diff.max().item() < 5e-3
+
+
 def test_rank_failure_ends_the_job_without_hanging(tmp_path):
     out = str(tmp_path / "never.pt")
     t0 = time.time()

@@ -51,3 +51,21 @@ def test_p2p_and_nccl_zero1_match_single_gpu(tmp_path):
     # the two communication paths compute the same mean of the same bf16 gradients
     assert max(abs(x - y) for x, y in zip(n["losses"], p["losses"])) < 2e-2
     assert s["losses"][-1] < s["losses"][0]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_llama_p2p_zero1_matches_single_gpu(tmp_path):
+    """The LLaMA-3 family under ZeRO-1 on the in-kernel NVLink path (its parameter groups differ from GPT-2's: no biases, an untied
+    head in the shared group) against a single-GPU run with gradient accumulation."""
+    world = 2
+    single, p2p = str(tmp_path / "single.pt"), str(tmp_path / "p2p.pt")
+    r = launch(1, single, ["--device", "cuda", "--zero", "0", "--slots", str(world), "--family", "llama3"], 0)
+    assert r.returncode == 0, r.stdout[-3000:]
+    r = launch(world, p2p, ["--device", "cuda", "--zero", "1", "--slots", str(world), "--backend", "p2p", "--family", "llama3"], 29551,
+               env_extra={"LLMC_GEMM_2SM_MIN_TILES": "1"})
+    assert r.returncode == 0, r.stdout[-3000:]
+    s, p = torch.load(single), torch.load(p2p)
+    assert p["backend"] == "p2p" and p["zero"] == 1
+    assert max(abs(x - y) for x, y in zip(s["losses"], p["losses"])) < 3e-2, (s["losses"], p["losses"])
+    assert (s["params"] - p["params"]).abs().max().item() < 2e-2
+    assert s["losses"][-1] < s["losses"][0]
