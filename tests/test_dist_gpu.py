@@ -68,4 +68,3 @@ def test_llama_p2p_zero1_matches_single_gpu(tmp_path):
     assert p["backend"] == "p2p" and p["zero"] == 1
     assert max(abs(x - y) for x, y in zip(s["losses"], p["losses"])) < 3e-2, (s["losses"], p["losses"])
     assert (s["params"] - p["params"]).abs().max().item() < 2e-2
-    assert s["losses"][-1] < s["losses"][0]
