@@ -18,6 +18,6 @@ while true; do
         -v 250 -s 20000 -g 144 -h 1 \
         -b 16 -t 1024 -d 1048576 -r 0 -z 1 -c 0.1 -l 0.0006 -q 0.1 -u 700 \
         -n 200 -nk 5 -nm 5000 -sl 7.0 -sg 7.0 \
-        -y 1 -e "d48"
+        -y 1 -wd 1800 -e "d48"
     sleep 1
 done

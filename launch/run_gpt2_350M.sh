@@ -18,6 +18,6 @@ while true; do
         -v 250 -s 20000 -g 144 -h 1 \
         -b 64 -t 1024 -d 524288 -r 0 -z 1 -c 0.1 -l 0.0003 -q 0.0 -u 700 \
         -n 5000 -nk 5 -nm 50000 -sl 7.0 -sg 7.0 \
-        -y 1 -e "d24"
+        -y 1 -wd 1800 -e "d24"
     sleep 1
 done

@@ -18,6 +18,6 @@ while true; do
         -v 250 -s 20000 -g 144 -h 1 \
         -b 32 -t 1024 -d 524288 -r 0 -z 1 -c 0.1 -l 0.00025 -q 0.0 -u 700 \
         -n 4000 -nk 5 -nm 200000 -sl 7.0 -sg 7.0 \
-        -y 1 -e "d36"
+        -y 1 -wd 1800 -e "d36"
     sleep 1
 done

@@ -18,6 +18,6 @@ while true; do
         -v 250 -s 20000 -g 144 -h 1 \
         -b 32 -t 2048 -d 524288 -r 0 -z 1 -c 0.1 -l 0.0006 -q 0.1 -u 700 \
         -n 10000 -nk 5 -nm 100000 -sl 7.0 -sg 7.0 \
-        -y 1 -e "gpt3:c768"
+        -y 1 -wd 1800 -e "gpt3:c768"
     sleep 1
 done

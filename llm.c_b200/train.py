@@ -45,11 +45,12 @@ Options (same letters as the reference trainer):
   -sl <float> skip update if loss z-score above (0 = off)   -sg <float> same for the gradient norm
   -v <int> val_loss_every (20)  -m <int> val_max_steps (20)  -s <int> sample_every (20)  -g <int> genT (64)  -h <int> HellaSwag eval (0)
   -a <int> overfit a single batch (0)
-  -f <int> TF32 for fp32 (accepted for compatibility)   -w <int> fp32 master weights (1)   -ge <int> GELU fusion (accepted)
+  -f <int> TF32 matmuls in the fp32 device mode (1)   -w <int> fp32 master weights (1)   -ge <int> GELU fusion (accepted)
   -z <int> ZeRO stage 0|1 (0)   -r <int> recompute 0|1|2 (1)
   -pn <int> num processes  -pr <int> process rank  -pg <int> GPUs per node  -pi <str> init method mpi|tcp|fs  -ps <ip>  -pf <path>
 Extensions:  -dev cpu|cuda   -dt bf16|fp32   -cb nccl|p2p (communication backend of the multi-GPU step)
              -b2 <float> AdamW beta2 (0.95)   -gc <float> gradient clipping norm (1.0; 0 = off)   -hp / -tp HellaSwag / tokenizer paths
+             -wd <float> watchdog: end the process (exit code 17) if no optimizer step completes within this many seconds (0 = off)
 """
 
 
@@ -101,6 +102,7 @@ class TrainConfig:
     prefetch: bool = True
     beta2: float = 0.95
     grad_clip: float = 1.0
+    watchdog_s: float = 0.0       # > 0: end the process if no optimizer step completes within this many seconds
 
 
 _FLAGS = {
@@ -116,6 +118,7 @@ _FLAGS = {
     "-ps": ("server_ip", str), "-pf": ("fs_path", str), "-pp": ("fs_path", str), "-sl": ("skip_update_lossz", float),
     "-sg": ("skip_update_gradz", float), "-dev": ("device", str), "-dt": ("dtype", str), "-cb": ("comm_backend", str),
     "-hp": ("hellaswag_path", str), "-tp": ("tokenizer_path", str), "-b2": ("beta2", float), "-gc": ("grad_clip", float),
+    "-wd": ("watchdog_s", float),
 }
 
 
@@ -236,6 +239,8 @@ class Trainer:
         self._h2d_events = None
         self._sample_model = None
         self._have_batch = False
+        from .utils.watchdog import StepWatchdog
+        self.watchdog = StepWatchdog(c.output_log_dir, d.process_rank, d.num_processes, c.watchdog_s).start()
         m.allocate_activations(B, T)
         if self.device.type == "cuda":
             self._h2d_events = [torch.cuda.Event(), torch.cuda.Event()]
@@ -409,7 +414,17 @@ class Trainer:
             zl, zg = self.loss_detector.update(loss), self.norm_detector.update(gnorm)
         if self.dist.num_processes > 1:
             loss = pdist.host_float_sum(self.dist, loss) / self.dist.num_processes
+        if self.device.type == "cuda":
+            # a kernel that gave up a bounded wait (peer flag, mbarrier) left its reason in the status word; the device is
+            # idle here (the loss was just read back), so reading it costs one small copy
+            from . import _lib
+            status = _lib.read_status(clear=True)
+            if status != 0:
+                raise RuntimeError("a kernel reported an abandoned wait: status 0x%08x (code %d at 0x%x) in step %d on rank %d"
+                                   % (status, status >> 24, status & 0xFFFFFF, step, self.dist.process_rank))
         self.step += 1
+        if self.watchdog.timeout_s > 0 or self.watchdog.log_dir:
+            self.watchdog.beat(self.step)
         return dict(loss=loss, grad_norm=gnorm, lr=lr, skipped=skipped, zloss=zl, zgrad=zg)
 
     # ------------------------------------------------------------------ the loop
@@ -462,6 +477,7 @@ class Trainer:
         p("total average iteration speed: %.0f tok/s (EMA)" % self.ema_tokens_per_second)
 
     def close(self):
+        self.watchdog.stop()
         for l in (self.train_loader, self.val_loader, self.eval_loader):
             if l is not None:
                 l.close()
