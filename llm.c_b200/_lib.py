@@ -93,7 +93,8 @@ def cuda():
 def host():
     global _host
     if _host is None:
-        _host = _load("libllmc_host.so", "build_host")
+        override = os.environ.get("LLMC_HOST_LIB")          # e.g. a sanitizer build of csrc/host/host.cpp (see the tests)
+        _host = ctypes.CDLL(override) if override else _load("libllmc_host.so", "build_host")
     return _host
 
 
