@@ -84,27 +84,32 @@ DEVINL bool wait_flag_ge(const unsigned long long* p, unsigned long long want, u
     return true;
 }
 
-__global__ void __launch_bounds__(512)
+// Small CTAs on purpose (128 threads, about 40 registers, no shared memory): the kernel runs on a side stream while the backward
+// pass continues, and the backward kernels are persistent CTAs that fill an SM's shared memory and most of its registers.  A
+// reduce-scatter CTA of this size fits next to them, so it neither waits for an SM to drain nor keeps a compute CTA from starting.
+constexpr int RS_THREADS = 128;
+
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS, THREADS == RS_THREADS ? 10 : 1)
 reduce_scatter_kernel(PeerPtrs grads, PeerPtrs sig, SliceList sl, int rank, int N, float scale, int channel,
                       unsigned long long seq, float* __restrict__ norm_partials, int wait_peers, unsigned int* status) {
-    __shared__ float red[32];
-    __shared__ int ok_s;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     unsigned long long* my_sig = reinterpret_cast<unsigned long long*>(sig.p[rank]);
-    // 1. tell every peer that this rank's gradients of `channel` are final (block 0 only)
+    // 1. tell every peer that this rank's gradients of `channel` are final (one warp of block 0)
     if (blockIdx.x == 0 && threadIdx.x < N) {
         __threadfence_system();
         unsigned long long* peer = reinterpret_cast<unsigned long long*>(sig.p[threadIdx.x]);
         st_release_sys(peer + SIG_RS_BASE + channel * MAX_RANKS + rank, seq);
     }
-    // 2. wait for every peer's signal
-    if (threadIdx.x == 0) ok_s = 1;
-    __syncthreads();
-    if (wait_peers && threadIdx.x < N) {
-        if (!wait_flag_ge(my_sig + SIG_RS_BASE + channel * MAX_RANKS + threadIdx.x, seq, status, 0x700 + threadIdx.x)) ok_s = 0;
+    // 2. every warp waits for every peer's signal itself (lane p polls peer p): no shared memory, no block barrier
+    bool ok = true;
+    if (wait_peers) {
+        bool mine_ok = true;
+        if (lane < N) mine_ok = wait_flag_ge(my_sig + SIG_RS_BASE + channel * MAX_RANKS + lane, seq, status, 0x700 + lane);
+        ok = __all_sync(0xffffffffu, mine_ok);
     }
-    __syncthreads();
     float acc_sq = 0.f;
-    if (ok_s) {
+    if (ok) {
         bf16* mine = reinterpret_cast<bf16*>(grads.p[rank]);
         for (int s = 0; s < sl.count; s++) {
             const long long shard = sl.size[s] / N;
@@ -112,15 +117,21 @@ reduce_scatter_kernel(PeerPtrs grads, PeerPtrs sig, SliceList sl, int rank, int 
             const long long packs = shard >> 3;
             for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < packs; i += (long long)gridDim.x * blockDim.x) {
                 float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                bf16x8 v[MAX_RANKS];
+                // rank order, four peers' loads in flight at a time: the same sum on every run
                 #pragma unroll
-                for (int p = 0; p < MAX_RANKS; p++)
-                    if (p < N) v[p] = ld128cs(reinterpret_cast<const bf16*>(grads.p[p]) + base + i * 8);
-                #pragma unroll
-                for (int p = 0; p < MAX_RANKS; p++) {       // rank order: the same sum on every run
-                    if (p < N) {
+                for (int p0 = 0; p0 < MAX_RANKS; p0 += 4) {
+                    if (p0 < N) {
+                        bf16x8 v[4];
                         #pragma unroll
-                        for (int e = 0; e < 8; e++) sum[e] += __bfloat162float(v[p][e]);
+                        for (int k = 0; k < 4; k++)
+                            if (p0 + k < N) v[k] = ld128cs(reinterpret_cast<const bf16*>(grads.p[p0 + k]) + base + i * 8);
+                        #pragma unroll
+                        for (int k = 0; k < 4; k++) {
+                            if (p0 + k < N) {
+                                #pragma unroll
+                                for (int e = 0; e < 8; e++) sum[e] += __bfloat162float(v[k][e]);
+                            }
+                        }
                     }
                 }
                 bf16x8 o;
@@ -134,8 +145,9 @@ reduce_scatter_kernel(PeerPtrs grads, PeerPtrs sig, SliceList sl, int rank, int 
             }
         }
     }
-    acc_sq = block_sum(acc_sq, red);
-    if (threadIdx.x == 0 && norm_partials) norm_partials[blockIdx.x] = acc_sq;
+    // one partial sum of squares per warp (the host adds them all)
+    acc_sq = warp_sum(acc_sq);
+    if (lane == 0 && norm_partials) norm_partials[blockIdx.x * (THREADS / 32) + warp] = acc_sq;
 }
 
 __global__ void scalar_allreduce_kernel(PeerPtrs sig, float* __restrict__ inout, int rank, int N, unsigned long long seq,
@@ -277,8 +289,15 @@ extern "C" int llmc_p2p_set_wait_cycles(long long cycles) {
     return 0;
 }
 
+// LLMC_RS_THREADS=512 selects whole-SM CTAs for the reduce-scatter (for measurements of the difference); the default is 128.
+static int rs_threads() {
+    static int v = 0;
+    if (v == 0) { const char* e = getenv("LLMC_RS_THREADS"); v = (e && atoi(e) == 512) ? 512 : RS_THREADS; }
+    return v;
+}
+
 // Reduce-scatter (mean) of up to 16 slices of the gradient buffers. grad_ptrs / sig_ptrs: N device pointers (one per rank).
-// Every slice size must be a multiple of 8*N. norm_partials: `ctas` floats (may be null).
+// Every slice size must be a multiple of 8*N. norm_partials: llmc_p2p_rs_partials(ctas) floats (may be null).
 extern "C" int llmc_p2p_reduce_scatter(const unsigned long long* grad_ptrs, const unsigned long long* sig_ptrs, const long long* offs,
                                        const long long* sizes, int count, int rank, int N, int channel, unsigned long long seq,
                                        float* norm_partials, int ctas, int wait_peers, cudaStream_t stream) {
@@ -286,10 +305,14 @@ extern "C" int llmc_p2p_reduce_scatter(const unsigned long long* grad_ptrs, cons
     if (fill(&g, grad_ptrs, N) || fill(&s, sig_ptrs, N) || count > 16 || channel < 0 || channel >= 200) return -1;
     sl.count = count;
     for (int i = 0; i < count; i++) { sl.off[i] = offs[i]; sl.size[i] = sizes[i]; if (sizes[i] % (8 * N) || offs[i] % 8) return -2; }
-    reduce_scatter_kernel<<<ctas, 512, 0, stream>>>(g, s, sl, rank, N, 1.0f / N, channel, seq, norm_partials, wait_peers, llmc_status_ptr());
+    if (rs_threads() == 512) reduce_scatter_kernel<512><<<ctas, 512, 0, stream>>>(g, s, sl, rank, N, 1.0f / N, channel, seq, norm_partials, wait_peers, llmc_status_ptr());
+    else reduce_scatter_kernel<RS_THREADS><<<ctas, RS_THREADS, 0, stream>>>(g, s, sl, rank, N, 1.0f / N, channel, seq, norm_partials, wait_peers, llmc_status_ptr());
     CUDA_CHECK(cudaGetLastError());
     return 0;
 }
+
+// number of partial sums of squares a reduce-scatter launch of `ctas` CTAs writes
+extern "C" int llmc_p2p_rs_partials(int ctas) { return ctas * (rs_threads() / 32); }
 
 extern "C" int llmc_p2p_allreduce_scalar(const unsigned long long* sig_ptrs, float* inout, int rank, int N, unsigned long long seq,
                                          cudaStream_t stream) {

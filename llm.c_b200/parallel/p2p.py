@@ -11,6 +11,7 @@ Capability parity: multi_gpu_async_reduce_gradient, the ncclAllReduce of the nor
 gpt2_update in the reference (llmc/zero.cuh:528-551, train_gpt2.cu:1002-1030 and 1101-1120).
 """
 import ctypes
+import os
 
 import torch
 import torch.distributed as dist
@@ -37,6 +38,8 @@ def _cfg_lib():
         lib.llmc_p2p_adamw_allgather.argtypes = [P, P, P, P, P, P, ctypes.POINTER(_lib.TensorTable), I, I, F, F, F, F, I, F, P, F, U, P, I, I, P]
         lib.llmc_p2p_wait.restype = I
         lib.llmc_p2p_wait.argtypes = [P, I, I, I, I, U, P]
+        lib.llmc_p2p_rs_partials.restype = I
+        lib.llmc_p2p_rs_partials.argtypes = [I]
         lib.llmc_p2p_ag_flag_offset.restype = I
         lib.llmc_p2p_ag_flag_offset.argtypes = [I]
         lib.llmc_p2p_barrier.restype = I
@@ -117,9 +120,14 @@ class P2PBackend:
         self.c_params, self.c_grads, self.c_sig = _ptr_array(self.param_ptrs), _ptr_array(self.grad_ptrs), _ptr_array(self.sig_ptrs)
         dev = dist_cfg.device
         self.stream = torch.cuda.Stream(device=dev)
-        self.ctas = 32
+        self.ctas = 32                  # x 4 = CTAs of the fused update + gather, which runs alone after backward
+        # reduce-scatter: one small CTA per SM, resident next to the backward kernels' CTAs
+        self.rs_ctas = torch.cuda.get_device_properties(dev).multi_processor_count
+        if os.environ.get("LLMC_RS_THREADS") == "512":      # whole-SM CTAs, kept for measuring the difference
+            self.rs_ctas = 32
+        self.rs_partials = self.lib.llmc_p2p_rs_partials(self.rs_ctas)
         self.num_channels = model.cfg.num_layers + 1
-        self.norm_partials = torch.zeros(self.num_channels * self.ctas, dtype=torch.float32, device=dev)
+        self.norm_partials = torch.zeros(self.num_channels * self.rs_partials, dtype=torch.float32, device=dev)
         self.done_counter = torch.zeros(1, dtype=torch.int32, device=dev)
         self.seq = 0            # optimizer-step sequence number shared by all flags of a step
         self.scalar_seq = 0
@@ -140,9 +148,9 @@ class P2PBackend:
         sizes = (ctypes.c_longlong * len(slices))(*[s[1] for s in slices])
         self.stream.wait_stream(torch.cuda.current_stream())
         kernels._launches += 1
-        part = self.norm_partials[ch * self.ctas:(ch + 1) * self.ctas]
+        part = self.norm_partials[ch * self.rs_partials:(ch + 1) * self.rs_partials]
         check(self.lib.llmc_p2p_reduce_scatter(self.c_grads, self.c_sig, offs, sizes, len(slices), self.r, self.N, ch, self.seq,
-                                               ctypes.c_void_p(part.data_ptr()), self.ctas, 1,
+                                               ctypes.c_void_p(part.data_ptr()), self.rs_ctas, 1,
                                                ctypes.c_void_p(self.stream.cuda_stream)), "llmc_p2p_reduce_scatter")
 
     def _channel_of(self, slices):
