@@ -183,7 +183,7 @@ ln_bwd_col_kernel(bf16* __restrict__ dinp, float* __restrict__ partials, const b
                     v[hh] = r_;
                 }
                 res[k] = pack_bf16x2(v[0], v[1]);
-                if (COLSUM) { dc[i][2 * k] += v[0]; dc[i][2 * k + 1] += v[1]; }   // column sums of dinp, taken before its rounding to bf16
+                if (COLSUM) { dc[i][2 * k] += bf16lo(res[k]); dc[i][2 * k + 1] += bf16hi(res[k]); }   // what the consumer of dinp reads
             }
             if (p < npack) *reinterpret_cast<uint4*>(dinp + rbase + p * 8) = make_uint4(res[0], res[1], res[2], res[3]);
         }
@@ -294,7 +294,7 @@ int lnb_dispatch(bool acc, bool col, bf16* dinp, float* scratch, const bf16* dou
 }  // namespace
 
 // dinp (+)= dLN ; dweight, dbias (+)= column sums.  `scratch` holds llmc_layernorm_bwd_scratch floats.
-// If dcolsum is given it receives (+)= the column sums of the final dinp (summed in fp32 before dinp is rounded): when dinp is the residual-stream gradient, that
+// If dcolsum is given it receives (+)= the column sums of the final dinp: when dinp is the residual-stream gradient, that
 // is the bias gradient of the projection that wrote into the residual stream, obtained without another pass.  C <= 16384.
 extern "C" int llmc_layernorm_bwd(bf16* dinp, bf16* dweight, bf16* dbias, float* scratch, const bf16* dout, const bf16* inp,
                                   const bf16* weight, const float* mean, const float* rstd, int N, int C,
