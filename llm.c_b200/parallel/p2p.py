@@ -121,10 +121,10 @@ class P2PBackend:
         dev = dist_cfg.device
         self.stream = torch.cuda.Stream(device=dev)
         self.ctas = 32                  # x 4 = CTAs of the fused update + gather, which runs alone after backward
-        # reduce-scatter: one small CTA per SM, resident next to the backward kernels' CTAs
-        self.rs_ctas = torch.cuda.get_device_properties(dev).multi_processor_count
-        if os.environ.get("LLMC_RS_THREADS") == "512":      # whole-SM CTAs, kept for measuring the difference
-            self.rs_ctas = 32
+        # reduce-scatter: 32 whole-SM CTAs next to the backward pass (LLMC_RS_THREADS=128: one small CTA per SM instead)
+        self.rs_ctas = 32
+        if os.environ.get("LLMC_RS_THREADS") == "128":
+            self.rs_ctas = torch.cuda.get_device_properties(dev).multi_processor_count
         self.rs_partials = self.lib.llmc_p2p_rs_partials(self.rs_ctas)
         self.num_channels = model.cfg.num_layers + 1
         self.norm_partials = torch.zeros(self.num_channels * self.rs_partials, dtype=torch.float32, device=dev)
