@@ -48,7 +48,9 @@ def main():
     offs = (ctypes.c_longlong * slices)(*[i * per for i in range(slices)])
     sizes = (ctypes.c_longlong * slices)(*[per] * slices)
     ctas = 4 * torch.cuda.get_device_properties(dev).multi_processor_count
-    partials = torch.zeros(4 * ctas, device=dev)          # one partial sum of squares per warp of the reduce-scatter CTAs
+    lib.llmc_p2p_rs_partials.restype = ctypes.c_int
+    lib.llmc_p2p_rs_partials.argtypes = [ctypes.c_int]
+    partials = torch.zeros(lib.llmc_p2p_rs_partials(ctas), device=dev)      # one partial sum of squares per warp of the reduce-scatter CTAs
     norm_sq = torch.zeros(1, device=dev)
     counter = torch.zeros(1, dtype=torch.int32, device=dev)
     # shard views of the 16 slices (ZeRO-1 layout: rank r owns [r*per/N, (r+1)*per/N) of every slice)
