@@ -42,6 +42,17 @@ def case(op):
         }
         fn, bytes_ = fns[op]
         return fn, bytes_, flops
+    if op == "gemm_tf32":
+        Mt, Nt, Kt = 8192, 3072, 768
+        a32, b32, bias32 = torch.randn(Mt, Kt, device=DEV), torch.randn(Nt, Kt, device=DEV) * 0.02, torch.randn(Nt, device=DEV)
+        d32 = torch.empty(Mt, Nt, device=DEV)
+        return (lambda: K.gemm_tf32(d32, a32, b32, bias32)), 4.0 * (Mt * Kt + Nt * Kt + Mt * Nt), 2.0 * Mt * Nt * Kt
+    if op == "gemm_fwd_1cta":
+        # a problem with too few 256 x 256 tiles for the two-SM kernel: runs on the single-CTA kernel (128 x 256 tiles)
+        Ms, Ns, Ks = 2048, 2304, 768
+        a, w, b = _bf(Ms, Ks), _bf(Ns, Ks, scale=0.02), _bf(Ns)
+        out = torch.empty(Ms, Ns, device=DEV, dtype=torch.bfloat16)
+        return (lambda: K.matmul_forward(out, a, w, b)), 2.0 * (Ms * Ks + Ns * Ks + Ms * Ns), 2.0 * Ms * Ns * Ks
     if op in ("attn_fwd", "attn_bwd"):
         B, T, NH = 16, 1024, 12
         qkv, dout = _bf(B, T, 3 * NH * 64), _bf(B, T, NH * 64)
@@ -134,7 +145,7 @@ def case(op):
 
 OPS = ["gemm_fwd", "gemm_gelu", "gemm_dgrad", "gemm_dgelu", "gemm_wgrad", "attn_fwd", "attn_bwd", "ln_fwd", "fused_residual", "ln_bwd", "ln_bwd_colsum",
        "classifier", "encoder_fwd", "encoder_bwd", "adamw", "norm", "bias_grad", "gelu", "rms_fwd", "rms_fused_residual", "rms_bwd", "rope_fwd",
-       "rope_bwd", "swiglu_fwd", "swiglu_bwd"]
+       "rope_bwd", "swiglu_fwd", "swiglu_bwd", "gemm_tf32", "gemm_fwd_1cta"]
 
 
 def main(argv):
