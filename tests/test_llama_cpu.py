@@ -209,3 +209,39 @@ def test_trainer_runs_checkpoints_and_resumes_bit_exactly(tmp_path, capsys):
     t3.close()
     out = capsys.readouterr().out
     assert len(vislog.losses_from_stdout(out)) == 4 and "val loss" in out and "generating:" in out
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# against an independent implementation: Hugging Face's LlamaForCausalLM
+
+@pytest.mark.parametrize("scaled", [False, True])
+def test_logits_match_huggingface_llama_after_weight_conversion(scaled):
+    transformers = pytest.importorskip("transformers")
+    from llmc_b200.utils import llama_convert
+    kw = dict(vocab_size=200, hidden_size=64, intermediate_size=192, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+              max_position_embeddings=64, rms_norm_eps=1e-5, rope_theta=500000.0, tie_word_embeddings=False, attention_bias=False, mlp_bias=False)
+    if scaled:
+        kw["rope_scaling"] = {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                              "original_max_position_embeddings": 8192}
+    try:
+        hf_cfg = transformers.LlamaConfig(**kw)
+        torch.manual_seed(0)
+        hf = transformers.LlamaForCausalLM(hf_cfg).float().eval()
+    except Exception as e:            # a transformers release with a different configuration surface
+        pytest.skip("cannot build the Hugging Face model: %s" % e)
+    cfg = llama_convert.config_from_hf(hf_cfg)
+    assert cfg.hidden_dim == 192 and cfg.use_scaled_rope == scaled and cfg.num_kv_heads == 2
+    m = llama3.Llama(cfg, "cpu", torch.float32)
+    llama_convert.from_hf_state_dict(m, hf.state_dict())
+    g = torch.Generator().manual_seed(3)
+    tok = torch.randint(0, 200, (2, 32), generator=g)
+    with torch.no_grad():
+        want = hf(tok).logits
+    m.forward(tok.to(torch.int32))
+    got = m.logits()[..., :200]
+    assert torch.allclose(got, want, atol=2e-4, rtol=1e-3), (got - want).abs().max()
+    # and back: the exported state dict is the one we started from
+    back = llama_convert.to_hf_state_dict(m)
+    ref = hf.state_dict()
+    for k, v in back.items():
+        assert torch.equal(v, ref[k].float()), k
