@@ -1,5 +1,5 @@
 """Converts a model checkpoint of this framework (or of the reference: same format) into a Hugging Face
-``GPT2LMHeadModel`` (reference: dev/eval/export_hf.py).
+``GPT2LMHeadModel`` (reference: dev/eval/export_hf.py), or a LLaMA-3 model file into a ``LlamaForCausalLM``.
 
     python -m llmc_b200.utils.export_hf --input log/model_00010000.bin --output gpt2_export [--dtype bfloat16]
 
@@ -44,7 +44,31 @@ def to_hf_state_dict(cfg, w):
     return sd
 
 
+def export_llama(path, output, dtype="bfloat16"):
+    """A LLaMA-3 model file of this framework -> ``LlamaForCausalLM`` (query / key rows permuted to the rotate-half convention)."""
+    from transformers import LlamaConfig, LlamaForCausalLM
+    from ..models.llama3 import Llama
+    from . import llama_convert
+    cfg, _ = checkpoint.read_model_header(path)
+    m = Llama(cfg, "cpu", torch.float32)
+    checkpoint.load_model(path, m)
+    kw = dict(vocab_size=cfg.vocab_size, hidden_size=cfg.channels, intermediate_size=cfg.hidden_dim, num_hidden_layers=cfg.num_layers,
+              num_attention_heads=cfg.num_heads, num_key_value_heads=cfg.num_kv_heads, max_position_embeddings=cfg.max_seq_len,
+              rms_norm_eps=cfg.norm_eps, rope_theta=cfg.rope_theta, tie_word_embeddings=False, attention_bias=False, mlp_bias=False)
+    if cfg.use_scaled_rope:
+        kw["rope_scaling"] = {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                              "original_max_position_embeddings": 8192}
+    model = LlamaForCausalLM(LlamaConfig(**kw))
+    missing, unexpected = model.load_state_dict(llama_convert.to_hf_state_dict(m), strict=False)
+    assert not [k for k in missing if "rotary" not in k], missing
+    model = model.to(getattr(torch, dtype))
+    model.save_pretrained(output, max_shard_size="5GB")
+    return model
+
+
 def export(path, output, dtype="bfloat16"):
+    if checkpoint.model_family(path) == "llama3":
+        return export_llama(path, output, dtype)
     from transformers import GPT2Config, GPT2LMHeadModel
     cfg, w = load_tensors(path)
     hf_cfg = GPT2Config(vocab_size=cfg.vocab_size, n_positions=cfg.max_seq_len, n_ctx=cfg.max_seq_len, n_embd=cfg.channels,

@@ -245,3 +245,28 @@ def test_logits_match_huggingface_llama_after_weight_conversion(scaled):
     ref = hf.state_dict()
     for k, v in back.items():
         assert torch.equal(v, ref[k].float()), k
+
+
+def test_export_to_huggingface_directory_and_back(tmp_path):
+    transformers = pytest.importorskip("transformers")
+    from llmc_b200.utils import export_hf, llama_convert
+    cfg = llama3.config_from_descriptor("llama3:l=2,c=64,h=4,kv=2,t=64,v=200,m=32,f=1.0")
+    m = llama3.Llama(cfg, "cpu", torch.float32)
+    m.init_random(5)
+    path = str(tmp_path / "m.bin")
+    checkpoint.write_model(path, m)
+    try:
+        hf = export_hf.export(path, str(tmp_path / "hf"), "float32")
+    except Exception as e:
+        pytest.skip("cannot build the Hugging Face model: %s" % e)
+    assert os.path.exists(tmp_path / "hf" / "config.json")
+    tok = torch.randint(0, 200, (1, 16), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want = hf(tok).logits
+    m.forward(tok.to(torch.int32))
+    assert torch.allclose(m.logits()[..., :200], want, atol=2e-4, rtol=1e-3)
+    # the converter CLI path: local directory -> model file -> identical parameters
+    assert llama_convert.main(["--hf-dir", str(tmp_path / "hf"), "--out", str(tmp_path / "back.bin"), "--dtype", "float32"]) == 0
+    m2 = llama3.Llama(checkpoint.read_model_header(str(tmp_path / "back.bin"))[0], "cpu", torch.float32)
+    checkpoint.load_model(str(tmp_path / "back.bin"), m2)
+    assert torch.equal(m2.params_flat, m.params_flat)
