@@ -56,6 +56,7 @@ def build_parser():
     p.add_argument("--checkpoint_every", type=int, default=0)
     p.add_argument("--resume", type=int, default=0)
     p.add_argument("--write_tensors", type=int, default=0)
+    p.add_argument("--watchdog_s", type=float, default=0.0, help="end the process if no optimizer step completes within this many seconds")
     return p
 
 
@@ -73,7 +74,7 @@ def train_config(args):
         weight_decay=args.weight_decay, grad_clip=args.grad_clip, val_loss_every=args.val_loss_every, val_max_steps=args.val_max_steps,
         sample_every=args.sample_every, overfit_single_batch=args.overfit_single_batch, device=args.device, dtype=dtype,
         zero_stage=args.zero_stage, recompute=args.recompute, checkpoint_every=args.checkpoint_every, resume=args.resume,
-        tokenizer_path=args.tokenizer_path, beta2=0.95)
+        tokenizer_path=args.tokenizer_path, beta2=0.95, watchdog_s=args.watchdog_s)
 
 
 def write_debug_state(trainer, model_path, state_path):
