@@ -22,6 +22,7 @@
 
 #include <atomic>
 #include <condition_variable>
+#include <functional>
 #include <mutex>
 #include <string>
 #include <thread>
@@ -529,4 +530,60 @@ API double llmc_outlier_update(void* p, double v) {
     double mean = o->sum / W, var = o->sum_sq / W - mean * mean, sd = sqrt(var);
     if (sd == 0.0) return 0.0;
     return (v - mean) / sd;
+}
+
+// ---------------------------------------------------------------------------------------------
+// CPU matmul out[BT, OC] = inp[BT, C] * weight[OC, C]^T (+ bias): the straightforward loop nest and a register-tiled one, both
+// split over threads by rows, for the CPU micro-benchmark (the role of dev/cpu/matmul_forward.c in the reference).
+
+static void split_rows(int rows, int nthreads, const std::function<void(int, int)>& body) {
+    if (nthreads < 1) nthreads = 1;
+    if (nthreads == 1 || rows < 2 * nthreads) { body(0, rows); return; }
+    std::vector<std::thread> pool;
+    const int per = (rows + nthreads - 1) / nthreads;
+    for (int t = 0; t < nthreads; t++) {
+        const int lo = t * per, hi = lo + per < rows ? lo + per : rows;
+        if (lo < hi) pool.emplace_back(body, lo, hi);
+    }
+    for (auto& th : pool) th.join();
+}
+
+API void llmc_cpu_matmul_naive(float* out, const float* inp, const float* weight, const float* bias, int BT, int C, int OC, int nthreads) {
+    split_rows(BT, nthreads, [&](int lo, int hi) {
+        for (int r = lo; r < hi; r++) {
+            const float* x = inp + (size_t)r * C;
+            for (int o = 0; o < OC; o++) {
+                const float* w = weight + (size_t)o * C;
+                float acc = bias ? bias[o] : 0.0f;
+                for (int c = 0; c < C; c++) acc += x[c] * w[c];
+                out[(size_t)r * OC + o] = acc;
+            }
+        }
+    });
+}
+
+// Eight input rows share every weight row that is streamed in: eight accumulators live in registers, so the weight matrix is read
+// once per eight rows instead of once per row.
+API void llmc_cpu_matmul_tiled(float* out, const float* inp, const float* weight, const float* bias, int BT, int C, int OC, int nthreads) {
+    constexpr int R = 8;
+    split_rows((BT + R - 1) / R, nthreads, [&](int lo, int hi) {
+        for (int blk = lo; blk < hi; blk++) {
+            const int r0 = blk * R, nr = r0 + R <= BT ? R : BT - r0;
+            for (int o = 0; o < OC; o++) {
+                const float* w = weight + (size_t)o * C;
+                float acc[R];
+                for (int k = 0; k < R; k++) acc[k] = bias ? bias[o] : 0.0f;
+                if (nr == R) {
+                    for (int c = 0; c < C; c++) {
+                        const float wv = w[c];
+                        for (int k = 0; k < R; k++) acc[k] += inp[(size_t)(r0 + k) * C + c] * wv;
+                    }
+                } else {
+                    for (int c = 0; c < C; c++)
+                        for (int k = 0; k < nr; k++) acc[k] += inp[(size_t)(r0 + k) * C + c] * w[c];
+                }
+                for (int k = 0; k < nr; k++) out[(size_t)(r0 + k) * OC + o] = acc[k];
+            }
+        }
+    });
 }

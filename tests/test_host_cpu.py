@@ -266,3 +266,15 @@ def test_training_loop_end_to_end(tmp_path, capsys):
     log = vislog.parse_logfile(str(tmp_path / "runB" / "main.log"))
     assert sorted(log["trl"]) == [0, 1, 2, 3] and 4 in log["tel"]
     assert os.path.exists(tmp_path / "runB" / "DONE_00000004") and not os.path.exists(tmp_path / "runB" / "model_00000002.bin")
+
+
+def test_cpu_matmul_kernels_match_torch():
+    """The two CPU matmuls of the host library (plain and register-tiled), odd sizes and thread counts included."""
+    from llmc_b200 import bench_cpu_matmul as bm
+    g = torch.Generator().manual_seed(0)
+    for BT, C, OC, threads in ((13, 24, 17, 1), (64, 48, 40, 3), (9, 8, 8, 4)):
+        inp, w, b = torch.randn(BT, C, generator=g), torch.randn(OC, C, generator=g), torch.randn(OC, generator=g)
+        ref = inp @ w.t() + b
+        for kind in ("naive", "tiled"):
+            assert torch.allclose(bm.matmul(kind, inp, w, b, threads), ref, atol=1e-4, rtol=1e-4), (kind, BT, C, OC)
+        assert torch.allclose(bm.matmul("tiled", inp, w, None, threads), inp @ w.t(), atol=1e-4, rtol=1e-4)
