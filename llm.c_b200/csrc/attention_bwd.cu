@@ -15,9 +15,10 @@
 // cuDNN (llmc/cudnn_att.cpp:186-191).
 //
 // Both MMA kernels are persistent (one CTA per SM walks a heavy-first list of work items; resident tiles and
-// TMEM accumulators are double buffered across items).  A CTA has 576 threads: warp 0 TMA producer, warp 1 MMA issuer, warps 2..17 softmax/epilogue
-// (thread = one row x one 32-column quarter).  The softmax threads pull S/dP into registers and release
-// the TMEM tiles at once, so the next tile's S/dP MMAs run underneath the exponentials.
+// TMEM accumulators are double buffered across items).  A CTA has 608 threads: warp 0 TMA producer, warp 1 issuer of the score
+// products (S, dP), warps 2..17 softmax/epilogue (thread = one row x one 32-column quarter), warp 18 issuer of the accumulating
+// products (dV, dK or dQ).  The softmax threads pull S/dP into registers and release the TMEM tiles at once, so the next
+// tile's S/dP MMAs run underneath the exponentials.
 //
 // Capability parity: attention_backward_cudnn (llmc/cudnn_att.cpp:256-288) and attention_backward
 // of llmc/attention.cuh in the reference.
@@ -349,7 +350,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constant
                 if (lane == 0) mbar_arrive(pds_full);
                 if (fetch_next) { lse_l2 = nxt_lse * log2e; dlt_s = nxt_dlt * a.scale; row_ok = nxt_ok; }
             }
-            // ---- item epilogue: accumulators -> global; the MMA warp is already working on the next item
+            // ---- item epilogue: accumulators -> global; the issuing warps are already working on the next item
             const int ab = it % ACCBUF;
             ok = mbar_wait(&acc_full[ab], (it / ACCBUF) & 1, abort_flag, a.status, 0x622) && ok;
             tc_fence_after();
