@@ -118,16 +118,18 @@ reduce_scatter_kernel(PeerPtrs grads, PeerPtrs sig, SliceList sl, int rank, int 
             const long long packs = shard >> 3;
             for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < packs; i += (long long)gridDim.x * blockDim.x) {
                 float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                // rank order, four peers' loads in flight at a time: the same sum on every run
+                // rank order: the same sum on every run.  The whole-SM CTAs keep all peers' loads in flight at once (NVLink latency
+                // is what this loop hides); the small CTAs have the registers for four at a time.
+                constexpr int GROUP = THREADS == RS_THREADS ? 4 : MAX_RANKS;
                 #pragma unroll
-                for (int p0 = 0; p0 < MAX_RANKS; p0 += 4) {
+                for (int p0 = 0; p0 < MAX_RANKS; p0 += GROUP) {
                     if (p0 < N) {
-                        bf16x8 v[4];
+                        bf16x8 v[GROUP];
                         #pragma unroll
-                        for (int k = 0; k < 4; k++)
+                        for (int k = 0; k < GROUP; k++)
                             if (p0 + k < N) v[k] = ld128cs(reinterpret_cast<const bf16*>(grads.p[p0 + k]) + base + i * 8);
                         #pragma unroll
-                        for (int k = 0; k < 4; k++) {
+                        for (int k = 0; k < GROUP; k++) {
                             if (p0 + k < N) {
                                 #pragma unroll
                                 for (int e = 0; e < 8; e++) sum[e] += __bfloat162float(v[k][e]);
