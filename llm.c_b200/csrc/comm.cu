@@ -102,12 +102,13 @@ reduce_scatter_kernel(PeerPtrs grads, PeerPtrs sig, SliceList sl, int rank, int 
         unsigned long long* peer = reinterpret_cast<unsigned long long*>(sig.p[threadIdx.x]);
         st_release_sys(peer + SIG_RS_BASE + channel * MAX_RANKS + rank, seq);
     }
-    // 2. every warp waits for every peer's signal itself (lane p polls peer p): no shared memory, no block barrier
+    // 2. the first warp waits for every peer's signal (lane p polls peer p; few pollers: every poll is a system-scope load that
+    //    goes to L2); the verdict reaches the other warps through the barrier itself, so no shared memory is needed
     bool ok = true;
     if (wait_peers) {
         bool mine_ok = true;
-        if (lane < N) mine_ok = wait_flag_ge(my_sig + SIG_RS_BASE + channel * MAX_RANKS + lane, seq, status, 0x700 + lane);
-        ok = __all_sync(0xffffffffu, mine_ok);
+        if (warp == 0 && lane < N) mine_ok = wait_flag_ge(my_sig + SIG_RS_BASE + channel * MAX_RANKS + lane, seq, status, 0x700 + lane);
+        ok = __syncthreads_and(mine_ok) != 0;
     }
     float acc_sq = 0.f;
     if (ok) {
