@@ -45,6 +45,8 @@ def cuda():
         "llmc_status_read": (I, [I, POINTER(c_uint)]),
         "llmc_tensormap_cache_clear": (None, []),
         "llmc_device_sm_count": (I, []),
+        "llmc_alloc_device_or_managed": (I, [POINTER(c_void_p), ctypes.c_size_t, I, POINTER(c_int)]),
+        "llmc_free_device_or_managed": (I, [P]),
         "llmc_gemm": (I, [P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, P, I, S]),
         "llmc_gemm2": (I, [P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, P, S]),
         "llmc_gemm2_after_flags": (I, [P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, P, P, I, U64, S]),
@@ -69,6 +71,8 @@ def cuda():
         "llmc_rope_bwd": (I, [P, P, P, L, I, I, I, I, S]),
         "llmc_swiglu_fwd": (I, [P, P, L, I, S]),
         "llmc_swiglu_bwd": (I, [P, P, P, L, I, S]),
+        "llmc_rope_cache": (I, [P, P, P, P, P, I, I, I, I, I, I, I, I, S]),
+        "llmc_cached_attention": (I, [P, P, P, P, I, I, I, I, I, I, I, S]),
         "llmc_gelu_bwd_inplace": (I, [P, P, L, S]),
         "llmc_residual_add": (I, [P, P, P, L, S]),
         "llmc_bias_grad_scratch": (L, [I, I]),

@@ -1,0 +1,161 @@
+// Incremental decoding with a key / value cache (the inference path of the reference's LLaMA script,
+// train_llama3.py:167-190 and :476-556: keys and values of earlier positions are kept, only the new tokens run through
+// the network).  Two kernels; both are memory-bound and small, so they use plain loads, no tensor cores:
+//
+//   rope_cache      raw (N, (NH + 2 NKV) * HS), N = B * Tq new tokens at positions start_pos .. start_pos + Tq - 1
+//                     -> q (N, NH, HS) rotated queries
+//                     -> kcache / vcache (B, Tmax, NKV, HS): rotated keys and the values written at their positions
+//   cached_attention  out (N, NH, HS) = softmax(q . K[0 .. pos] / sqrt(HS)) V[0 .. pos] per (batch row, new token, head);
+//                     grouped queries read the cache head h / (NH / NKV) directly, nothing is expanded.
+#include "common.cuh"
+
+namespace {
+
+DEVINL bf16x8 rotate8(const bf16x8& a, const float4& cs0, const float4& cs1) {
+    bf16x8 r;
+    const float c[4] = {cs0.x, cs0.z, cs1.x, cs1.z};
+    const float s[4] = {cs0.y, cs0.w, cs1.y, cs1.w};
+    #pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const float re = __bfloat162float(a[2 * j]), im = __bfloat162float(a[2 * j + 1]);
+        r[2 * j] = __float2bfloat16_rn(re * c[j] - im * s[j]);
+        r[2 * j + 1] = __float2bfloat16_rn(re * s[j] + im * c[j]);
+    }
+    return r;
+}
+
+__global__ void __launch_bounds__(256)
+rope_cache_kernel(bf16* __restrict__ q, bf16* __restrict__ kcache, bf16* __restrict__ vcache, const bf16* __restrict__ raw,
+                  const float2* __restrict__ freqs, long long N, int Tq, int Tmax, int start_pos, int NH, int NKV, int HS) {
+    const int hp = HS >> 3;
+    const int heads = NH + 2 * NKV;
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= N * heads * hp) return;
+    const int p = (int)(idx % hp);
+    const int h = (int)((idx / hp) % heads);
+    const long long n = idx / ((long long)hp * heads);
+    const int pos = start_pos + (int)(n % Tq);
+    const long long b = n / Tq;
+    bf16x8 a = ld128cs(raw + (n * heads + h) * HS + p * 8);
+    if (h < NH + NKV) {
+        const float4* f = reinterpret_cast<const float4*>(freqs + (size_t)pos * (HS >> 1) + p * 4);
+        a = rotate8(a, f[0], f[1]);
+    }
+    if (h < NH) {
+        st128(q + (n * NH + h) * HS + p * 8, a);
+    } else if (h < NH + NKV) {
+        st128(kcache + ((b * Tmax + pos) * NKV + (h - NH)) * HS + p * 8, a);
+    } else {
+        st128(vcache + ((b * Tmax + pos) * NKV + (h - NH - NKV)) * HS + p * 8, a);
+    }
+}
+
+constexpr int DEC_THREADS = 128;
+constexpr int DEC_CHUNK = 512;      // keys whose scores sit in shared memory at a time (running maximum across chunks)
+constexpr int DEC_MAX_HS = 128;
+
+// One CTA per (head, new token, batch row).  Scores: a thread per key, the query in shared memory as fp32 (already scaled).
+// Weighted sum of the values: a thread per pair of channels, DEC_THREADS / (HS / 2) key groups side by side, folded at the end.
+__global__ void __launch_bounds__(DEC_THREADS)
+cached_attention_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, const bf16* __restrict__ kcache,
+                        const bf16* __restrict__ vcache, int Tq, int Tmax, int start_pos, int NH, int NKV, int HS, float scale) {
+    __shared__ float qs[DEC_MAX_HS];
+    __shared__ float sc[DEC_CHUNK];
+    __shared__ float red[32];
+    __shared__ float part[DEC_THREADS * 2];
+    const int tid = threadIdx.x;
+    const int h = blockIdx.x, t = blockIdx.y;
+    const long long b = blockIdx.z;
+    const long long n = b * Tq + t;
+    const int g = h / (NH / NKV);
+    const int nkeys = start_pos + t + 1;
+    if (tid < HS) qs[tid] = __bfloat162float(q[(n * NH + h) * HS + tid]) * scale;
+    __syncthreads();
+    const int pairs = HS >> 1;
+    const int groups = DEC_THREADS / pairs;
+    const int my_pair = tid % pairs, my_group = tid / pairs;
+    const int hp = HS >> 3;
+    float m = -INFINITY, l = 0.f, acc0 = 0.f, acc1 = 0.f;
+    for (int base = 0; base < nkeys; base += DEC_CHUNK) {
+        const int cnt = min(DEC_CHUNK, nkeys - base);
+        float lmax = -INFINITY;
+        for (int j = tid; j < cnt; j += DEC_THREADS) {
+            const bf16* krow = kcache + ((b * Tmax + base + j) * NKV + g) * HS;
+            float s = 0.f;
+            for (int p = 0; p < hp; p++) {
+                const bf16x8 kk = ld128(krow + p * 8);
+                #pragma unroll
+                for (int e = 0; e < 8; e++) s += qs[p * 8 + e] * __bfloat162float(kk[e]);
+            }
+            sc[j] = s;
+            lmax = fmaxf(lmax, s);
+        }
+        const float m_new = fmaxf(m, block_max(lmax, red));
+        float lsum = 0.f;
+        for (int j = tid; j < cnt; j += DEC_THREADS) {
+            const float pj = __expf(sc[j] - m_new);
+            sc[j] = pj;
+            lsum += pj;
+        }
+        const float csum = block_sum(lsum, red);
+        const float corr = __expf(m - m_new);
+        l = l * corr + csum;
+        acc0 *= corr;
+        acc1 *= corr;
+        m = m_new;
+        if (my_group < groups) {
+            for (int j = my_group; j < cnt; j += groups) {
+                const bf16* vrow = vcache + ((b * Tmax + base + j) * NKV + g) * HS;
+                const float2 vv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(vrow + 2 * my_pair));
+                acc0 += sc[j] * vv.x;
+                acc1 += sc[j] * vv.y;
+            }
+        }
+        __syncthreads();
+    }
+    part[tid * 2] = (my_group < groups) ? acc0 : 0.f;
+    part[tid * 2 + 1] = (my_group < groups) ? acc1 : 0.f;
+    __syncthreads();
+    if (tid < pairs) {
+        float o0 = 0.f, o1 = 0.f;
+        for (int gi = 0; gi < groups; gi++) {
+            o0 += part[(gi * pairs + tid) * 2];
+            o1 += part[(gi * pairs + tid) * 2 + 1];
+        }
+        const float inv = 1.0f / l;
+        *reinterpret_cast<__nv_bfloat162*>(out + (n * NH + h) * HS + 2 * tid) = __floats2bfloat162_rn(o0 * inv, o1 * inv);
+    }
+}
+
+int decode_check(int B, int Tq, int Tmax, int start_pos, int NH, int NKV, int HS) {
+    if (HS % 8 || HS > DEC_MAX_HS || HS < 16 || NKV <= 0 || NH % NKV) return -1;
+    if (B <= 0 || Tq <= 0 || start_pos < 0 || start_pos + Tq > Tmax) return -2;
+    if (B > 65535 || Tq > 65535) return -3;
+    return 0;
+}
+
+}  // namespace
+
+// freqs holds (cos, sin) for freqs_len positions; every position written must lie inside it and inside the cache.
+extern "C" int llmc_rope_cache(bf16* q, bf16* kcache, bf16* vcache, const bf16* raw, const float* freqs, int freqs_len, int B, int Tq,
+                               int Tmax, int start_pos, int NH, int NKV, int HS, cudaStream_t stream) {
+    const int rc = decode_check(B, Tq, Tmax, start_pos, NH, NKV, HS);
+    if (rc) return rc;
+    if (start_pos + Tq > freqs_len) return -4;
+    const long long N = (long long)B * Tq;
+    const long long total = N * (NH + 2 * NKV) * (HS / 8);
+    rope_cache_kernel<<<(unsigned)CEIL_DIV(total, 256), 256, 0, stream>>>(q, kcache, vcache, raw, reinterpret_cast<const float2*>(freqs),
+                                                                          N, Tq, Tmax, start_pos, NH, NKV, HS);
+    CUDA_CHECK(cudaGetLastError());
+    return 0;
+}
+
+extern "C" int llmc_cached_attention(bf16* out, const bf16* q, const bf16* kcache, const bf16* vcache, int B, int Tq, int Tmax,
+                                     int start_pos, int NH, int NKV, int HS, cudaStream_t stream) {
+    const int rc = decode_check(B, Tq, Tmax, start_pos, NH, NKV, HS);
+    if (rc) return rc;
+    const dim3 grid(NH, Tq, B);
+    cached_attention_kernel<<<grid, DEC_THREADS, 0, stream>>>(out, q, kcache, vcache, Tq, Tmax, start_pos, NH, NKV, HS, rsqrtf((float)HS));
+    CUDA_CHECK(cudaGetLastError());
+    return 0;
+}

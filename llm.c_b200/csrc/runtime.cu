@@ -116,3 +116,38 @@ extern "C" int llmc_device_sm_count() {
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
     return n;
 }
+
+// ----------------------------------------------------------------------------
+// Device memory when it fits, managed memory otherwise.
+//
+// Optimizer state is touched once per step, so when the device is full it can live in managed memory whose preferred home is
+// the host: the update kernel then reads and writes it across the host link instead of the run ending with an allocation
+// error (capability parity with cudaMallocConditionallyManaged, llmc/cuda_utils.cuh:213-229 of the reference).
+// *managed is set to 1 if the fallback was taken.  force_managed skips the device attempt (used by the tests).
+extern "C" int llmc_alloc_device_or_managed(void** out, size_t bytes, int force_managed, int* managed) {
+    if (!out || !managed || bytes == 0) return -1;
+    *out = nullptr;
+    *managed = 0;
+    if (!force_managed) {
+        cudaError_t e = cudaMalloc(out, bytes);
+        if (e == cudaSuccess) return 0;
+        (void)cudaGetLastError();                       // clear the sticky-free allocation error before trying again
+        if (e != cudaErrorMemoryAllocation) {
+            fprintf(stderr, "[llmc_b200] cudaMalloc(%zu): %s\n", bytes, cudaGetErrorString(e));
+            return -1;
+        }
+    }
+    int dev = 0;
+    CUDA_CHECK(cudaGetDevice(&dev));
+    CUDA_CHECK(cudaMallocManaged(out, bytes, cudaMemAttachGlobal));
+    // advice is best effort: a platform that rejects it still has working managed memory
+    if (cudaMemAdvise(*out, bytes, cudaMemAdviseSetPreferredLocation, cudaCpuDeviceId) != cudaSuccess) (void)cudaGetLastError();
+    if (cudaMemAdvise(*out, bytes, cudaMemAdviseSetAccessedBy, dev) != cudaSuccess) (void)cudaGetLastError();
+    *managed = 1;
+    return 0;
+}
+
+extern "C" int llmc_free_device_or_managed(void* p) {
+    if (p) CUDA_CHECK(cudaFree(p));
+    return 0;
+}

@@ -304,6 +304,28 @@ def swiglu_backward(dx12, dh, x12):
     check(_lib.cuda().llmc_swiglu_bwd(_p(dx12), _p(dh), _p(x12), N, H, _stream()), "llmc_swiglu_bwd")
 
 
+def rope_cache(q, kcache, vcache, raw, freqs, Tq, start_pos, NH, NKV):
+    """Rotary embedding of the Tq new tokens per batch row at positions start_pos.., queries to ``q`` (N, NH, HS), rotated keys
+    and the values into their slots of the caches (B, Tmax, NKV, HS) (reference: CausalSelfAttention.forward with
+    ``use_kv``, train_llama3.py:167-180)."""
+    global _launches
+    N = raw.shape[0]
+    HS = raw.shape[1] // (NH + 2 * NKV)
+    _launches += 1
+    check(_lib.cuda().llmc_rope_cache(_p(q), _p(kcache), _p(vcache), _p(raw), _p(freqs), freqs.shape[0], N // Tq, Tq, kcache.shape[1],
+                                      start_pos, NH, NKV, HS, _stream()), "llmc_rope_cache")
+
+
+def cached_attention(out, q, kcache, vcache, Tq, start_pos, NH, NKV):
+    """out (N, NH, HS): causal attention of the Tq new queries per batch row over cache positions 0 .. start_pos + t."""
+    global _launches
+    N = q.shape[0]
+    HS = kcache.shape[-1]
+    _launches += 1
+    check(_lib.cuda().llmc_cached_attention(_p(out), _p(q), _p(kcache), _p(vcache), N // Tq, Tq, kcache.shape[1], start_pos, NH, NKV,
+                                            HS, _stream()), "llmc_cached_attention")
+
+
 def make_table(views):
     """views: list of dicts(p_base, p_stride, o_base, o_stride, n, L, wd, seed[, l_base])."""
     tab = TensorTable()

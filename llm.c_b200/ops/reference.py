@@ -331,6 +331,34 @@ def rope_backward(draw, dpacked, freqs, T, NH, NKV):
     draw.copy_(torch.cat([dq, dk, dv], dim=1).view(N, -1))
 
 
+def rope_cache(q, kcache, vcache, raw, freqs, Tq, start_pos, NH, NKV):
+    N = raw.shape[0]
+    B = N // Tq
+    HS = raw.shape[1] // (NH + 2 * NKV)
+    x = _f(raw).view(N, NH + 2 * NKV, HS)
+    f = freqs[start_pos:start_pos + Tq]
+    q.view(N, NH, HS).copy_(_rotate(x[:, :NH], f, Tq, 1.0))
+    kcache[:B, start_pos:start_pos + Tq].copy_(_rotate(x[:, NH:NH + NKV], f, Tq, 1.0).view(B, Tq, NKV, HS))
+    vcache[:B, start_pos:start_pos + Tq].copy_(x[:, NH + NKV:].view(B, Tq, NKV, HS))
+
+
+def cached_attention(out, q, kcache, vcache, Tq, start_pos, NH, NKV):
+    N = q.shape[0]
+    B = N // Tq
+    HS = kcache.shape[-1]
+    rep = NH // NKV
+    S = start_pos + Tq
+    qq = _f(q).view(B, Tq, NH, HS).transpose(1, 2)                                    # (B, NH, Tq, HS)
+    k = _f(kcache[:B, :S]).repeat_interleave(rep, dim=2).transpose(1, 2)              # (B, NH, S, HS)
+    v = _f(vcache[:B, :S]).repeat_interleave(rep, dim=2).transpose(1, 2)
+    att = qq @ k.transpose(-1, -2) / math.sqrt(HS)
+    key = torch.arange(S, device=att.device).view(1, S)
+    qry = torch.arange(Tq, device=att.device).view(Tq, 1) + start_pos
+    att = att.masked_fill(key > qry, float("-inf"))
+    y = torch.softmax(att, dim=-1) @ v                                                # (B, NH, Tq, HS)
+    out.view(B, Tq, NH, HS).copy_(y.transpose(1, 2))
+
+
 def swiglu_forward(h, x12):
     H = h.shape[1]
     x = _f(x12)

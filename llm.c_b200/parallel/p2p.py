@@ -99,6 +99,10 @@ class ParamSync:
     def wait(self, layer):
         self.backend.wait_params(layer + 1)
 
+    def wait_all(self):
+        """Every group, for readers outside the training forward pass (generation, checkpoints)."""
+        self.backend.wait_params()
+
     def flags(self, layer):
         if self.backend.published_seq == 0:
             return None

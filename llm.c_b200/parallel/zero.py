@@ -122,9 +122,13 @@ class ShardedAdamW:
         div = self.N if self.sharded else 1
         self.shard_num_parameters = model.num_parameters // div
         dev = model.device
-        self.m = torch.zeros(self.shard_num_parameters, dtype=torch.float32, device=dev)
-        self.v = torch.zeros(self.shard_num_parameters, dtype=torch.float32, device=dev)
-        self.master = torch.zeros(self.shard_num_parameters, dtype=torch.float32, device=dev) if self.use_master else None
+        # optimizer state falls back to managed memory when the device is full (utils/memory.py)
+        from ..utils.memory import zeros_device_or_managed
+        n = self.shard_num_parameters
+        self.m, m_managed = zeros_device_or_managed(n, torch.float32, dev, "AdamW first moment")
+        self.v, v_managed = zeros_device_or_managed(n, torch.float32, dev, "AdamW second moment")
+        self.master, w_managed = zeros_device_or_managed(n, torch.float32, dev, "master weights") if self.use_master else (None, False)
+        self.state_in_managed_memory = m_managed or v_managed or w_managed
         self.master_initialized = False
         self.norm_sq = torch.zeros(1, dtype=torch.float32, device=dev)
         self.sampler = Sampler(13371337 + self.r)          # stochastic-rounding seed stream

@@ -238,6 +238,7 @@ class Trainer:
         self.telemetry = None
         self._h2d_events = None
         self._sample_model = None
+        self._sample_gen = None
         self._have_batch = False
         from .utils.watchdog import StepWatchdog
         self.watchdog = StepWatchdog(c.output_log_dir, d.process_rank, d.num_processes, c.watchdog_s).start()
@@ -353,6 +354,14 @@ class Trainer:
     def sample(self, genT):
         """Autoregressive sampling on rank 0 (full prefix recomputed per token, as in the reference train_gpt2.cu:1752-1796)."""
         m = self.model
+        if getattr(m, "family", "") == "llama3":
+            # key / value cache, nucleus sampling at the reference script's settings (train_llama3.py:1172)
+            from .models.generate import generate
+            if self._sample_gen is None:
+                self._sample_gen = torch.Generator().manual_seed(1337)
+            start = min(128000, m.cfg.vocab_size - 1)                       # <|begin_of_text|>
+            stops = [t for t in (128001, 128009) if t < m.cfg.vocab_size]   # <|end_of_text|>, <|eot_id|>
+            return generate(m, [[start]], max(genT - 1, 1), temperature=0.6, top_p=0.9, stop_tokens=stops, generator=self._sample_gen)[0]
         if self._sample_model is None:
             # a second model object over the same parameter buffer, with its own (small) activation set
             sm = type(m)(m.cfg, self.device, m.dtype, recompute=2, flat_allocator=lambda kind, numel, dt: m.params_flat)

@@ -211,6 +211,27 @@ def test_trainer_runs_checkpoints_and_resumes_bit_exactly(tmp_path, capsys):
     assert len(vislog.losses_from_stdout(out)) == 4 and "val loss" in out and "generating:" in out
 
 
+def test_script_generates_from_prompt_tokens(tmp_path, capsys):
+    """--inference_only of the LLaMA script: batched prompts given as token ids, with and without the key / value cache."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("train_llama3_script", os.path.join(os.path.dirname(__file__), "..", "train_llama3.py"))
+    script = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(script)
+    _files(tmp_path)
+    common = ["--model", TDESC, "--input_bin", str(tmp_path / "train.bin"), "--input_val_bin", str(tmp_path / "val.bin"),
+              "--batch_size", "2", "--sequence_length", "16", "--total_batch_size", "32", "--device", "cpu", "--dtype", "float32",
+              "--inference_only", "1", "--prompt_tokens", "5,6,7;9", "--max_gen_len", "6", "--temperature", "0",
+              "--tokenizer_path", str(tmp_path / "none.bin")]
+    outs = []
+    for kv in ("1", "0"):
+        assert script.main(common + ["--use_kv", kv]) == 0
+        lines = [l for l in capsys.readouterr().out.splitlines() if l.startswith("generated token ids:")]
+        assert len(lines) == 2
+        outs.append(lines)
+    assert outs[0] == outs[1]
+    assert all(len(l.split(":")[1].split()) == 6 for l in outs[0])
+
+
 # ---------------------------------------------------------------------------------------------------------------
 # against an independent implementation: Hugging Face's LlamaForCausalLM
 

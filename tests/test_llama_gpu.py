@@ -166,3 +166,58 @@ def test_gpu_training_reduces_loss_and_is_deterministic():
     l1, p1 = runs[1]
     assert l0[0] > math.log(1000) - 0.5 and l0[-1] < l0[0] - 0.5, l0
     assert l0 == l1 and torch.equal(p0, p1), "two identical runs must agree bit for bit"
+
+
+@pytest.mark.parametrize("B,Tq,start,Tmax,NH,NKV,HS", [(2, 5, 0, 16, 4, 2, 64), (3, 1, 700, 1024, 8, 2, 128), (1, 9, 40, 64, 6, 3, 96),
+                                                       (2, 3, 5, 16, 4, 4, 64), (1, 2, 1100, 1200, 2, 1, 64)])
+def test_decoding_kernels(B, Tq, start, Tmax, NH, NKV, HS):
+    """Rotary embedding into the cache and attention over the cache against the fp32 restatement (also beyond one 512-key
+    chunk of the running softmax)."""
+    cfg = llama3.LlamaConfig(max_seq_len=Tmax, num_heads=NH, num_kv_heads=NKV, channels=NH * HS)
+    freqs = llama3.rope_table(cfg)
+    N, QR = B * Tq, (NH + 2 * NKV) * HS
+    raw = rnd(N, QR)
+    kc, vc = rnd(B, Tmax, NKV, HS, seed=1), rnd(B, Tmax, NKV, HS, seed=2)
+    rq, rk, rv = torch.zeros(N, NH * HS), kc.float().clone(), vc.float().clone()
+    R.rope_cache(rq, rk, rv, raw, freqs, Tq, start, NH, NKV)
+    q = torch.zeros(N, NH * HS, dtype=torch.bfloat16, device=DEV)
+    dk, dv = kc.to(DEV), vc.to(DEV)
+    KN.rope_cache(q, dk, dv, raw.to(DEV), freqs.to(DEV), Tq, start, NH, NKV)
+    close(q, rq, 2e-2, 1e-2, "rope_cache q")
+    close(dk, rk, 2e-2, 1e-2, "rope_cache k")
+    assert torch.equal(dv.cpu()[:, start:start + Tq], raw.view(B, Tq, NH + 2 * NKV, HS)[:, :, NH + NKV:])
+    assert torch.equal(dv.cpu()[:, :start], vc[:, :start])                 # nothing else is touched
+    ro = torch.zeros(N, NH * HS)
+    R.cached_attention(ro, q.cpu(), dk.cpu(), dv.cpu(), Tq, start, NH, NKV)
+    out = torch.full((N, NH * HS), float("nan"), dtype=torch.bfloat16, device=DEV)
+    KN.cached_attention(out, q, dk, dv, Tq, start, NH, NKV)
+    close(out, ro, 2e-2, 2e-2, "cached_attention")
+
+
+def test_cached_decoder_and_generate():
+    """The bf16 decoder on the GPU against the fp32 CPU decoder over the same (bf16-rounded) weights, and generation with the
+    cache against generation that recomputes the prefix."""
+    from llmc_b200.models import generate as G
+    cfg = llama3.config_from_descriptor("llama3:l=2,c=256,h=4,kv=2,t=128,v=500,m=64,f=1.0")
+    m = llama3.Llama(cfg, DEV, torch.bfloat16, recompute=1)
+    m.init_random(3)
+    for n in ("qkvw", "attprojw", "fc12w", "fcprojw"):
+        m.params[n].mul_(3.0)
+    c = llama3.Llama(cfg, "cpu", torch.float32, recompute=0)
+    c.params_flat.copy_(m.params_flat.float().cpu())
+    g = torch.Generator().manual_seed(0)
+    tok = torch.randint(0, cfg.vocab_size, (3, 40), generator=g, dtype=torch.int32)
+    dm, dc = G.CachedDecoder(m, 3, 64), G.CachedDecoder(c, 3, 64)
+    close(dm.forward(tok[:, :33].contiguous().to(DEV), 0), dc.forward(tok[:, :33].contiguous(), 0), 3e-2, 3e-2, "prefill logits")
+    for t in range(33, 40):
+        got, want = dm.forward(tok[:, t:t + 1].contiguous().to(DEV), t), dc.forward(tok[:, t:t + 1].contiguous(), t)
+    close(got, want, 3e-2, 3e-2, "decode logits")
+    # the training forward pass of the same model agrees on the last position
+    m.forward(tok.to(DEV))
+    close(got, m.logits()[:, -1, :cfg.vocab_size], 3e-2, 3e-2, "decode vs training forward")
+    prompts = [[5, 9, 11, 3], [7, 2], list(range(20, 50))]
+    a = G.generate(m, prompts, max_gen_len=12, temperature=0.0, echo=True)
+    b = G.generate(m, prompts, max_gen_len=12, temperature=0.0, echo=True, use_kv=False)
+    assert a == b
+    for p, out in zip(prompts, a):
+        assert out[:len(p)] == p and len(out) == len(p) + 12

@@ -128,3 +128,26 @@ def test_fp32_mode_with_tf32_kernel_tracks_the_cpu_path():
             assert (got - want).abs().max().item() < 0.02 * scale + 1e-5, name
     finally:
         torch.backends.cuda.matmul.allow_tf32 = False
+
+
+def test_optimizer_state_in_managed_memory_trains_identically(monkeypatch):
+    """The fallback placement of the AdamW moments and master weights (managed memory that prefers the host) changes where the
+    state lives, not what the update computes."""
+    runs = []
+    for force in ("0", "1"):
+        monkeypatch.setenv("LLMC_FORCE_MANAGED", force)
+        m = make("cuda", torch.bfloat16, 0)
+        opt = ShardedAdamW(m, DistConfig(0, 1, 0, torch.device("cuda", 0)), 0, True)
+        assert opt.state_in_managed_memory == (force == "1")
+        x, y = batch(m.cfg, 2, 128)
+        x, y = x.cuda(), y.cuda()
+        for step in range(3):
+            m.forward(x, y)
+            m.backward()
+            opt.grad_norm_sq()
+            opt.step(3e-3, 0.1, step + 1)
+        torch.cuda.synchronize()
+        runs.append((m.params_flat.clone(), opt.m.clone(), opt.master.clone()))
+        del opt, m
+    for a, b in zip(runs[0], runs[1]):
+        assert torch.equal(a, b)

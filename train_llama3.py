@@ -56,6 +56,12 @@ def build_parser():
     p.add_argument("--checkpoint_every", type=int, default=0)
     p.add_argument("--resume", type=int, default=0)
     p.add_argument("--write_tensors", type=int, default=0)
+    p.add_argument("--prompt_tokens", type=str, default="", help="prompts for --inference_only as token ids, e.g. '128000,9906;128000,791' "
+                   "(the tokenizer file of this framework only decodes)")
+    p.add_argument("--max_gen_len", type=int, default=64)
+    p.add_argument("--temperature", type=float, default=0.6)
+    p.add_argument("--top_p", type=float, default=0.9)
+    p.add_argument("--use_kv", type=int, default=1, help="0: recompute the prefix for every token instead of caching keys and values")
     p.add_argument("--watchdog_s", type=float, default=0.0, help="end the process if no optimizer step completes within this many seconds")
     return p
 
@@ -109,6 +115,20 @@ def write_debug_state(trainer, model_path, state_path):
     return loss
 
 
+def generate_from_args(model, args):
+    """Batched generation as in the reference's sampling block (train_llama3.py:1150-1178), prompts given as token ids."""
+    from llmc_b200.models.generate import generate
+    V = model.cfg.vocab_size
+    if args.prompt_tokens:
+        prompts = [[int(t) for t in row.split(",") if t.strip()] for row in args.prompt_tokens.split(";") if row.strip()]
+    else:
+        prompts = [[min(128000, V - 1)]]
+    stops = [t for t in (128001, 128009) if t < V]
+    gen = torch.Generator().manual_seed(1337)
+    return generate(model, prompts, args.max_gen_len, temperature=args.temperature, top_p=args.top_p, stop_tokens=stops,
+                    generator=gen, use_kv=bool(args.use_kv))
+
+
 def main(argv=None):
     args = build_parser().parse_args(argv)
     cfg = train_config(args)
@@ -123,9 +143,9 @@ def main(argv=None):
         if args.inference_only:
             if trainer.val_loader is not None:
                 trainer.print0("val loss %f" % trainer.validate())
-            toks = trainer.sample(max(trainer.cfg.genT, 16))
-            if toks is not None:
-                trainer.print0("generated token ids: " + " ".join(str(int(t)) for t in toks))
+            if trainer.dist.process_rank == 0:
+                for toks in generate_from_args(trainer.model, args):
+                    trainer.print0("generated token ids: " + " ".join(str(int(t)) for t in toks))
         else:
             trainer.run()
     finally:
