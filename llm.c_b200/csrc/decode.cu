@@ -7,6 +7,10 @@
 //                     -> kcache / vcache (B, Tmax, NKV, HS): rotated keys and the values written at their positions
 //   cached_attention  out (N, NH, HS) = softmax(q . K[0 .. pos] / sqrt(HS)) V[0 .. pos] per (batch row, new token, head);
 //                     grouped queries read the cache head h / (NH / NKV) directly, nothing is expanded.
+//
+// start_pos comes from the host or, when `pos_ptr` is given, from device memory: a decoding step captured in a CUDA graph is
+// replayed with the position advanced on the device.  A device position that would leave the cache or the rotary table makes
+// the kernel record ST_BAD_ARG in the status word and return without touching memory.
 #include "common.cuh"
 
 namespace {
@@ -26,7 +30,15 @@ DEVINL bf16x8 rotate8(const bf16x8& a, const float4& cs0, const float4& cs1) {
 
 __global__ void __launch_bounds__(256)
 rope_cache_kernel(bf16* __restrict__ q, bf16* __restrict__ kcache, bf16* __restrict__ vcache, const bf16* __restrict__ raw,
-                  const float2* __restrict__ freqs, long long N, int Tq, int Tmax, int start_pos, int NH, int NKV, int HS) {
+                  const float2* __restrict__ freqs, long long N, int Tq, int Tmax, int start_pos, int NH, int NKV, int HS,
+                  const int* __restrict__ pos_ptr, int freqs_len, unsigned int* status) {
+    if (pos_ptr) {
+        start_pos = *pos_ptr;
+        if (start_pos < 0 || start_pos + Tq > Tmax || start_pos + Tq > freqs_len) {
+            if (threadIdx.x == 0 && blockIdx.x == 0) record_error(status, ST_BAD_ARG, 0x30);
+            return;
+        }
+    }
     const int hp = HS >> 3;
     const int heads = NH + 2 * NKV;
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -58,7 +70,15 @@ constexpr int DEC_MAX_HS = 128;
 // Weighted sum of the values: a thread per pair of channels, DEC_THREADS / (HS / 2) key groups side by side, folded at the end.
 __global__ void __launch_bounds__(DEC_THREADS)
 cached_attention_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, const bf16* __restrict__ kcache,
-                        const bf16* __restrict__ vcache, int Tq, int Tmax, int start_pos, int NH, int NKV, int HS, float scale) {
+                        const bf16* __restrict__ vcache, int Tq, int Tmax, int start_pos, int NH, int NKV, int HS, float scale,
+                        const int* __restrict__ pos_ptr, unsigned int* status) {
+    if (pos_ptr) {
+        start_pos = *pos_ptr;
+        if (start_pos < 0 || start_pos + Tq > Tmax) {
+            if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) record_error(status, ST_BAD_ARG, 0x31);
+            return;
+        }
+    }
     __shared__ float qs[DEC_MAX_HS];
     __shared__ float sc[DEC_CHUNK];
     __shared__ float red[32];
@@ -127,9 +147,75 @@ cached_attention_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
     }
 }
 
-int decode_check(int B, int Tq, int Tmax, int start_pos, int NH, int NKV, int HS) {
+// ---------------------------------------------------------------------------------------------------------------
+// Skinny product for decoding steps: out (M, N) = x (M, K) . w (N, K)^T with M <= 8 rows.  A 128-row tensor-core tile would
+// spend its time on padding and, worse, leave most SMs without a tile (N / 128 tiles for 148 SMs), while the step is bound by
+// streaming the weights once.  Here every warp owns SK_COLS output columns, its lanes stride over K with 128-bit streaming
+// loads (SK_UNROLL per column in flight), the few activation rows come through L1, and products accumulate in fp32.
+constexpr int SK_THREADS = 128;
+constexpr int SK_COLS = 2;
+constexpr int SK_UNROLL = 4;
+constexpr int SK_MAX_M = 8;
+
+template <int MM>
+__global__ void __launch_bounds__(SK_THREADS)
+skinny_gemm_kernel(bf16* __restrict__ out, const bf16* __restrict__ x, const bf16* __restrict__ w, int M, int N, int K,
+                   int ldx, int ldw, int ldo) {
+    const int lane = threadIdx.x & 31;
+    const int warp = blockIdx.x * (SK_THREADS / 32) + (threadIdx.x >> 5);
+    const int n0 = warp * SK_COLS;
+    if (n0 >= N) return;
+    float acc[MM][SK_COLS];
+    #pragma unroll
+    for (int m = 0; m < MM; m++)
+        #pragma unroll
+        for (int c = 0; c < SK_COLS; c++) acc[m][c] = 0.f;
+    const bf16* wrow[SK_COLS];
+    #pragma unroll
+    for (int c = 0; c < SK_COLS; c++) wrow[c] = w + (size_t)min(n0 + c, N - 1) * ldw;      // a clamped column is computed, not stored
+    for (int kb = lane * 8; kb < K; kb += 32 * 8 * SK_UNROLL) {
+        bf16x8 wv[SK_UNROLL][SK_COLS];
+        #pragma unroll
+        for (int u = 0; u < SK_UNROLL; u++) {
+            const int k = kb + u * 256;
+            #pragma unroll
+            for (int c = 0; c < SK_COLS; c++) wv[u][c] = (k < K) ? ld128cs(wrow[c] + k) : bf16x8::zeros();
+        }
+        #pragma unroll
+        for (int u = 0; u < SK_UNROLL; u++) {
+            const int k = kb + u * 256;
+            if (k >= K) break;
+            #pragma unroll
+            for (int m = 0; m < MM; m++) {
+                if (m < M) {
+                    const bf16x8 xv = ld128(x + (size_t)m * ldx + k);
+                    #pragma unroll
+                    for (int e = 0; e < 8; e++) {
+                        const float xe = __bfloat162float(xv[e]);
+                        #pragma unroll
+                        for (int c = 0; c < SK_COLS; c++) acc[m][c] += xe * __bfloat162float(wv[u][c][e]);
+                    }
+                }
+            }
+        }
+    }
+    #pragma unroll
+    for (int m = 0; m < MM; m++)
+        #pragma unroll
+        for (int c = 0; c < SK_COLS; c++) acc[m][c] = warp_sum(acc[m][c]);
+    if (lane == 0) {
+        #pragma unroll
+        for (int m = 0; m < MM; m++)
+            #pragma unroll
+            for (int c = 0; c < SK_COLS; c++)
+                if (m < M && n0 + c < N) out[(size_t)m * ldo + n0 + c] = __float2bfloat16_rn(acc[m][c]);
+    }
+}
+
+int decode_check(int B, int Tq, int Tmax, int start_pos, int NH, int NKV, int HS, bool device_pos) {
     if (HS % 8 || HS > DEC_MAX_HS || HS < 16 || NKV <= 0 || NH % NKV) return -1;
-    if (B <= 0 || Tq <= 0 || start_pos < 0 || start_pos + Tq > Tmax) return -2;
+    if (B <= 0 || Tq <= 0 || Tq > Tmax) return -2;
+    if (!device_pos && (start_pos < 0 || start_pos + Tq > Tmax)) return -2;
     if (B > 65535 || Tq > 65535) return -3;
     return 0;
 }
@@ -137,25 +223,39 @@ int decode_check(int B, int Tq, int Tmax, int start_pos, int NH, int NKV, int HS
 }  // namespace
 
 // freqs holds (cos, sin) for freqs_len positions; every position written must lie inside it and inside the cache.
+// pos_ptr: null, or a device int that replaces start_pos when the kernel runs.
 extern "C" int llmc_rope_cache(bf16* q, bf16* kcache, bf16* vcache, const bf16* raw, const float* freqs, int freqs_len, int B, int Tq,
-                               int Tmax, int start_pos, int NH, int NKV, int HS, cudaStream_t stream) {
-    const int rc = decode_check(B, Tq, Tmax, start_pos, NH, NKV, HS);
+                               int Tmax, int start_pos, int NH, int NKV, int HS, const int* pos_ptr, cudaStream_t stream) {
+    const int rc = decode_check(B, Tq, Tmax, start_pos, NH, NKV, HS, pos_ptr != nullptr);
     if (rc) return rc;
-    if (start_pos + Tq > freqs_len) return -4;
+    if (!pos_ptr && start_pos + Tq > freqs_len) return -4;
     const long long N = (long long)B * Tq;
     const long long total = N * (NH + 2 * NKV) * (HS / 8);
     rope_cache_kernel<<<(unsigned)CEIL_DIV(total, 256), 256, 0, stream>>>(q, kcache, vcache, raw, reinterpret_cast<const float2*>(freqs),
-                                                                          N, Tq, Tmax, start_pos, NH, NKV, HS);
+                                                                          N, Tq, Tmax, start_pos, NH, NKV, HS, pos_ptr, freqs_len,
+                                                                          llmc_status_ptr());
     CUDA_CHECK(cudaGetLastError());
     return 0;
 }
 
 extern "C" int llmc_cached_attention(bf16* out, const bf16* q, const bf16* kcache, const bf16* vcache, int B, int Tq, int Tmax,
-                                     int start_pos, int NH, int NKV, int HS, cudaStream_t stream) {
-    const int rc = decode_check(B, Tq, Tmax, start_pos, NH, NKV, HS);
+                                     int start_pos, int NH, int NKV, int HS, const int* pos_ptr, cudaStream_t stream) {
+    const int rc = decode_check(B, Tq, Tmax, start_pos, NH, NKV, HS, pos_ptr != nullptr);
     if (rc) return rc;
     const dim3 grid(NH, Tq, B);
-    cached_attention_kernel<<<grid, DEC_THREADS, 0, stream>>>(out, q, kcache, vcache, Tq, Tmax, start_pos, NH, NKV, HS, rsqrtf((float)HS));
+    cached_attention_kernel<<<grid, DEC_THREADS, 0, stream>>>(out, q, kcache, vcache, Tq, Tmax, start_pos, NH, NKV, HS, rsqrtf((float)HS),
+                                                              pos_ptr, llmc_status_ptr());
+    CUDA_CHECK(cudaGetLastError());
+    return 0;
+}
+
+// out (M, N) = x (M, K) . w (N, K)^T for M <= 8; K and the row strides of x and w are multiples of 8 elements.
+extern "C" int llmc_skinny_gemm(bf16* out, const bf16* x, const bf16* w, int M, int N, int K, int ldx, int ldw, int ldo, cudaStream_t stream) {
+    if (M <= 0 || M > SK_MAX_M || N <= 0 || K <= 0 || (K % 8) || (ldx % 8) || (ldw % 8)) return -1;
+    const int warps = CEIL_DIV(N, SK_COLS);
+    const unsigned grid = (unsigned)CEIL_DIV(warps, SK_THREADS / 32);
+    if (M <= 4) skinny_gemm_kernel<4><<<grid, SK_THREADS, 0, stream>>>(out, x, w, M, N, K, ldx, ldw, ldo);
+    else skinny_gemm_kernel<8><<<grid, SK_THREADS, 0, stream>>>(out, x, w, M, N, K, ldx, ldw, ldo);
     CUDA_CHECK(cudaGetLastError());
     return 0;
 }

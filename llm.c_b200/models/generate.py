@@ -7,9 +7,12 @@ sampling is nucleus (top-p) at a temperature, or greedy at temperature 0.
 
 The decoder works on the parameter tensors of a ``models.llama3.Llama`` (it never copies them), with its own small activation
 set and the caches ``(L, max_batch, max_len, NKV, HS)``.  On a GPU every step is a chain of this library's kernels: the GEMMs
-of training (rows padded to one 128-row tile), RMSNorm / SwiGLU, and the two decoding kernels of csrc/decode.cu (rotary
+of training for prompts (rows padded to one 128-row tile) or a weight-streaming product for steps of at most 8 rows, RMSNorm / SwiGLU, and the two decoding kernels of csrc/decode.cu (rotary
 embedding written straight into the cache; attention of the new queries over the cached keys with grouped heads read in
-place).  On the CPU the same chain runs on the fp32 restatement of the operators.
+place).  A one-token step issues about nine small launches per layer and is bound by launch latency, so on a GPU it is
+captured once in a CUDA graph and replayed (``GraphStep``): the position lives in device memory, the graph advances it itself,
+and the kernels refuse a position outside the cache through the library's status word.  On the CPU the same chain runs on
+the fp32 restatement of the operators.
 """
 import torch
 
@@ -28,6 +31,8 @@ class CachedDecoder:
         self.vcache = torch.zeros_like(self.kcache)
         self._rows = 0
         self._bufs = None
+        # steps of at most this many rows use the weight-streaming product instead of a padded tensor-core tile (0: never)
+        self.skinny_rows = 8 if (model.device.type == "cuda" and model.dtype == torch.bfloat16) else 0
 
     def cache_bytes(self):
         return 2 * self.kcache.numel() * self.kcache.element_size()
@@ -47,36 +52,73 @@ class CachedDecoder:
             self._rows = rows
         return self._bufs, rows
 
-    def forward(self, tokens, start_pos):
+    def forward(self, tokens, start_pos, pos=None):
         """tokens (B, Tq) int32 on the model's device: the tokens at positions start_pos .. start_pos + Tq - 1 of every row.
-        Returns the fp32 logits (B, vocab_size) of the last of them; keys and values of all of them enter the cache."""
+        Returns the fp32 logits (B, vocab_size) of the last of them; keys and values of all of them enter the cache.
+        With ``pos`` (one int32 on the device) the position is read by the kernels when they run and start_pos is ignored."""
         m = self.model
         cfg, p = m.cfg, m.params
         B, Tq = tokens.shape
-        if B > self.max_batch or start_pos + Tq > self.max_len:
+        if B > self.max_batch or (pos is None and start_pos + Tq > self.max_len):
             raise ValueError("batch %d / positions up to %d exceed the cache (%d, %d)" % (B, start_pos + Tq, self.max_batch, self.max_len))
-        if m.param_sync is not None:
-            m.param_sync.wait_all()
+        if m.param_sync is not None and pos is None:
+            m.param_sync.wait_all()            # (a replayed step follows a prefill that has waited already)
         N = B * Tq
         a, rows = self._buffers(N, B)
         L, NH, NKV, eps, C = cfg.num_layers, cfg.num_heads, cfg.num_kv_heads, cfg.norm_eps, cfg.channels
         x, ln, rstd = a["x"], a["ln"], a["rstd"]
+        padded = m.device.type == "cuda"
+
+        def mm(out, inp, weight, n):
+            if n <= self.skinny_rows:
+                ops.matmul_skinny(out[:n], inp[:n], weight)
+            elif padded:
+                ops.matmul_forward(out, inp, weight, None)          # whole 128-row tiles; the rows beyond n are never read
+            else:
+                ops.matmul_forward(out[:n], inp[:n], weight, None)
+
         ops.encoder_forward(x[:N].view(B, Tq, C), tokens, p["wte"], None)
         ops.rmsnorm_forward(ln[:N], rstd[:N], x[:N], p["ln1w"][0], eps)
         for l in range(L):
-            ops.matmul_forward(a["raw"], ln, p["qkvw"][l], None)
-            ops.rope_cache(a["q"][:N], self.kcache[l], self.vcache[l], a["raw"][:N], m.freqs, Tq, start_pos, NH, NKV)
-            ops.cached_attention(a["atty"][:N], a["q"][:N], self.kcache[l], self.vcache[l], Tq, start_pos, NH, NKV)
-            ops.matmul_forward(a["proj"], a["atty"], p["attprojw"][l], None)
+            mm(a["raw"], ln, p["qkvw"][l], N)
+            ops.rope_cache(a["q"][:N], self.kcache[l], self.vcache[l], a["raw"][:N], m.freqs, Tq, start_pos, NH, NKV, pos)
+            ops.cached_attention(a["atty"][:N], a["q"][:N], self.kcache[l], self.vcache[l], Tq, start_pos, NH, NKV, pos)
+            mm(a["proj"], a["atty"], p["attprojw"][l], N)
             ops.rmsnorm_fused_residual_forward(a["res"][:N], ln[:N], rstd[:N], x[:N], a["proj"][:N], p["ln2w"][l], eps)
-            ops.matmul_forward(a["fc12"], ln, p["fc12w"][l], None)
-            ops.swiglu_forward(a["h"], a["fc12"])
-            ops.matmul_forward(a["proj"], a["h"], p["fcprojw"][l], None)
+            mm(a["fc12"], ln, p["fc12w"][l], N)
+            ops.swiglu_forward(a["h"][:N], a["fc12"][:N])
+            mm(a["proj"], a["h"], p["fcprojw"][l], N)
             w = p["ln1w"][l + 1] if l + 1 < L else p["lnfw"]
             ops.rmsnorm_fused_residual_forward(x[:N], ln[:N], rstd[:N], a["res"][:N], a["proj"][:N], w, eps)
         a["last"][:B].copy_(ln[:N].view(B, Tq, C)[:, -1])
-        ops.matmul_forward(a["logits"], a["last"], p["lmhead"], None)
+        mm(a["logits"], a["last"], p["lmhead"], B)
         return a["logits"][:B, :cfg.vocab_size].float()
+
+
+class GraphStep:
+    """The one-token step of a ``CachedDecoder`` for a fixed batch size, captured in a CUDA graph.  ``step(tokens)`` copies the
+    (B, 1) tokens into the graph's input, replays it and returns the graph's logits tensor (B, vocab_size), which the next
+    replay overwrites.  The graph ends by adding 1 to the device-resident position."""
+
+    def __init__(self, decoder, batch, start_pos):
+        dev = decoder.model.device
+        self.decoder = decoder
+        self.tokens = torch.zeros(batch, 1, dtype=torch.int32, device=dev)
+        self.pos = torch.full((1,), start_pos, dtype=torch.int32, device=dev)
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            decoder.forward(self.tokens, 0, pos=self.pos)      # buffers, tensor maps and kernel attributes exist before the capture;
+        torch.cuda.current_stream(dev).wait_stream(side)       # what it wrote at start_pos is overwritten by the first real step
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.logits = decoder.forward(self.tokens, 0, pos=self.pos)
+            self.pos.add_(1)
+
+    def step(self, tokens):
+        self.tokens.copy_(tokens.view_as(self.tokens), non_blocking=True)
+        self.graph.replay()
+        return self.logits
 
 
 def sample_top_p(probs, top_p, generator=None):
@@ -91,10 +133,11 @@ def sample_top_p(probs, top_p, generator=None):
 
 
 def generate(model, prompt_tokens, max_gen_len, temperature=0.6, top_p=0.9, echo=False, stop_tokens=(), pad_id=-1,
-             generator=None, use_kv=True, decoder=None):
+             generator=None, use_kv=True, decoder=None, use_graph=None):
     """prompt_tokens: list of token-id lists.  Returns the list of generated id lists (with the prompt in front if ``echo``),
     each cut at its first stop token.  ``use_kv=False`` recomputes the whole prefix at every step through the same decoder
-    (the slow path the cache replaces; it exists to check the cache against)."""
+    (the slow path the cache replaces; it exists to check the cache against).  ``use_graph`` (default: on for a CUDA model)
+    replays the one-token steps from a CUDA graph."""
     cfg = model.cfg
     bsz = len(prompt_tokens)
     lens = [len(t) for t in prompt_tokens]
@@ -106,6 +149,10 @@ def generate(model, prompt_tokens, max_gen_len, temperature=0.6, top_p=0.9, echo
     if decoder is None:
         decoder = CachedDecoder(model, bsz, total_len)
     dev = model.device
+    if use_graph is None:
+        use_graph = dev.type == "cuda"
+    use_graph = bool(use_graph) and use_kv and dev.type == "cuda"
+    graph_step = None
     tokens = torch.full((bsz, total_len), pad_id, dtype=torch.int64)
     for i, t in enumerate(prompt_tokens):
         tokens[i, :len(t)] = torch.tensor(t, dtype=torch.int64)
@@ -116,7 +163,12 @@ def generate(model, prompt_tokens, max_gen_len, temperature=0.6, top_p=0.9, echo
     for cur in range(min(lens), total_len):
         lo = prev if use_kv else 0
         step_in = tokens[:, lo:cur].clamp(min=0).to(torch.int32).to(dev)      # positions below cur are always filled
-        logits = decoder.forward(step_in, lo).cpu()
+        if use_graph and lo > 0 and cur - lo == 1:
+            if graph_step is None:
+                graph_step = GraphStep(decoder, bsz, lo)
+            logits = graph_step.step(step_in).cpu()
+        else:
+            logits = decoder.forward(step_in, lo).cpu()
         if temperature > 0:
             nxt = sample_top_p(torch.softmax(logits / temperature, dim=-1), top_p, generator)
         else:

@@ -20,7 +20,7 @@ _NAMES = [
     "fused_classifier", "gelu_forward", "gelu_backward_inplace", "residual_add", "global_norm_sq", "adamw_update",
     "params_from_master", "master_from_params",
     "rmsnorm_forward", "rmsnorm_fused_residual_forward", "rmsnorm_backward", "rope_forward", "rope_backward",
-    "swiglu_forward", "swiglu_backward", "rope_cache", "cached_attention",
+    "swiglu_forward", "swiglu_backward", "rope_cache", "cached_attention", "matmul_skinny",
 ]
 
 

@@ -304,26 +304,37 @@ def swiglu_backward(dx12, dh, x12):
     check(_lib.cuda().llmc_swiglu_bwd(_p(dx12), _p(dh), _p(x12), N, H, _stream()), "llmc_swiglu_bwd")
 
 
-def rope_cache(q, kcache, vcache, raw, freqs, Tq, start_pos, NH, NKV):
+def rope_cache(q, kcache, vcache, raw, freqs, Tq, start_pos, NH, NKV, pos=None):
     """Rotary embedding of the Tq new tokens per batch row at positions start_pos.., queries to ``q`` (N, NH, HS), rotated keys
     and the values into their slots of the caches (B, Tmax, NKV, HS) (reference: CausalSelfAttention.forward with
-    ``use_kv``, train_llama3.py:167-180)."""
+    ``use_kv``, train_llama3.py:167-180).  ``pos`` (a one-element int32 device tensor) replaces start_pos at run time, for
+    steps that are replayed from a CUDA graph."""
     global _launches
     N = raw.shape[0]
     HS = raw.shape[1] // (NH + 2 * NKV)
     _launches += 1
     check(_lib.cuda().llmc_rope_cache(_p(q), _p(kcache), _p(vcache), _p(raw), _p(freqs), freqs.shape[0], N // Tq, Tq, kcache.shape[1],
-                                      start_pos, NH, NKV, HS, _stream()), "llmc_rope_cache")
+                                      start_pos, NH, NKV, HS, _p(pos), _stream()), "llmc_rope_cache")
 
 
-def cached_attention(out, q, kcache, vcache, Tq, start_pos, NH, NKV):
+def cached_attention(out, q, kcache, vcache, Tq, start_pos, NH, NKV, pos=None):
     """out (N, NH, HS): causal attention of the Tq new queries per batch row over cache positions 0 .. start_pos + t."""
     global _launches
     N = q.shape[0]
     HS = kcache.shape[-1]
     _launches += 1
     check(_lib.cuda().llmc_cached_attention(_p(out), _p(q), _p(kcache), _p(vcache), N // Tq, Tq, kcache.shape[1], start_pos, NH, NKV,
-                                            HS, _stream()), "llmc_cached_attention")
+                                            HS, _p(pos), _stream()), "llmc_cached_attention")
+
+
+def matmul_skinny(out, inp, weight):
+    """out[M,OC] = inp[M,C] @ weight[OC,C]^T for at most 8 rows: the weight-streaming kernel of decoding steps (csrc/decode.cu)."""
+    global _launches
+    M, C = inp.shape
+    OC = weight.shape[0]
+    _launches += 1
+    check(_lib.cuda().llmc_skinny_gemm(_p(out), _p(inp), _p(weight), M, OC, C, inp.stride(0), weight.stride(0), out.stride(0), _stream()),
+          "llmc_skinny_gemm")
 
 
 def make_table(views):

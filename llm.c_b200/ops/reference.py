@@ -331,7 +331,9 @@ def rope_backward(draw, dpacked, freqs, T, NH, NKV):
     draw.copy_(torch.cat([dq, dk, dv], dim=1).view(N, -1))
 
 
-def rope_cache(q, kcache, vcache, raw, freqs, Tq, start_pos, NH, NKV):
+def rope_cache(q, kcache, vcache, raw, freqs, Tq, start_pos, NH, NKV, pos=None):
+    if pos is not None:
+        start_pos = int(pos.item())
     N = raw.shape[0]
     B = N // Tq
     HS = raw.shape[1] // (NH + 2 * NKV)
@@ -342,7 +344,9 @@ def rope_cache(q, kcache, vcache, raw, freqs, Tq, start_pos, NH, NKV):
     vcache[:B, start_pos:start_pos + Tq].copy_(x[:, NH + NKV:].view(B, Tq, NKV, HS))
 
 
-def cached_attention(out, q, kcache, vcache, Tq, start_pos, NH, NKV):
+def cached_attention(out, q, kcache, vcache, Tq, start_pos, NH, NKV, pos=None):
+    if pos is not None:
+        start_pos = int(pos.item())
     N = q.shape[0]
     B = N // Tq
     HS = kcache.shape[-1]
@@ -357,6 +361,10 @@ def cached_attention(out, q, kcache, vcache, Tq, start_pos, NH, NKV):
     att = att.masked_fill(key > qry, float("-inf"))
     y = torch.softmax(att, dim=-1) @ v                                                # (B, NH, Tq, HS)
     out.view(B, Tq, NH, HS).copy_(y.transpose(1, 2))
+
+
+def matmul_skinny(out, inp, weight):
+    out.copy_(_f(inp) @ _f(weight).t())
 
 
 def swiglu_forward(h, x12):

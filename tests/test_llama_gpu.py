@@ -216,8 +216,59 @@ def test_cached_decoder_and_generate():
     m.forward(tok.to(DEV))
     close(got, m.logits()[:, -1, :cfg.vocab_size], 3e-2, 3e-2, "decode vs training forward")
     prompts = [[5, 9, 11, 3], [7, 2], list(range(20, 50))]
-    a = G.generate(m, prompts, max_gen_len=12, temperature=0.0, echo=True)
-    b = G.generate(m, prompts, max_gen_len=12, temperature=0.0, echo=True, use_kv=False)
+    # bit-identical tokens need the same product kernel on both sides, so the weight-streaming product is switched off here
+    d1, d2 = G.CachedDecoder(m, 3, 42), G.CachedDecoder(m, 3, 42)
+    d1.skinny_rows = d2.skinny_rows = 0
+    a = G.generate(m, prompts, max_gen_len=12, temperature=0.0, echo=True, decoder=d1)
+    b = G.generate(m, prompts, max_gen_len=12, temperature=0.0, echo=True, use_kv=False, decoder=d2)
     assert a == b
+    assert len(G.generate(m, prompts, max_gen_len=12, temperature=0.0)[0]) == 12          # default path: skinny product + graph
     for p, out in zip(prompts, a):
         assert out[:len(p)] == p and len(out) == len(p) + 12
+
+
+def test_graph_replayed_decoding_step_equals_eager_and_refuses_positions_outside_the_cache():
+    from llmc_b200 import _lib
+    from llmc_b200.models import generate as G
+    cfg = llama3.config_from_descriptor("llama3:l=2,c=256,h=4,kv=2,t=64,v=500,m=64,f=1.0")
+    m = llama3.Llama(cfg, DEV, torch.bfloat16, recompute=1)
+    m.init_random(5)
+    g = torch.Generator().manual_seed(0)
+    tok = torch.randint(0, cfg.vocab_size, (2, 24), generator=g, dtype=torch.int32).to(DEV)
+    eager, graphed = G.CachedDecoder(m, 2, 32), G.CachedDecoder(m, 2, 32)
+    eager.forward(tok[:, :10].contiguous(), 0)
+    graphed.forward(tok[:, :10].contiguous(), 0)
+    gs = G.GraphStep(graphed, 2, 10)
+    for t in range(10, 24):
+        want = eager.forward(tok[:, t:t + 1].contiguous(), t)
+        got = gs.step(tok[:, t:t + 1])
+        assert torch.equal(got, want), "position %d" % t
+    assert int(gs.pos.item()) == 24
+    assert torch.equal(eager.kcache, graphed.kcache) and torch.equal(eager.vcache, graphed.vcache)
+    # whole generations agree with and without the graph
+    prompts = [[5, 9, 11, 3], [7, 2, 8]]
+    assert G.generate(m, prompts, 20, temperature=0.0, use_graph=True) == G.generate(m, prompts, 20, temperature=0.0, use_graph=False)
+    # a device position past the end of the cache: the kernels write nothing and say so in the status word
+    _lib.read_status(clear=True)
+    before = graphed.kcache.clone()
+    gs.pos.fill_(32)
+    gs.step(tok[:, :1])
+    status = _lib.read_status(clear=True)
+    assert status >> 24 == 3 and (status & 0xFFFFFF) in (0x30, 0x31), hex(status)
+    assert torch.equal(graphed.kcache, before)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 256, 512), (4, 515, 264), (8, 500, 4096), (5, 128, 8), (3, 6144, 2048)])
+def test_skinny_product(M, N, K):
+    x, w = rnd(M, K), rnd(N, K, scale=0.05, seed=1)
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    KN.matmul_skinny(out, x.to(DEV), w.to(DEV))
+    ref = torch.empty(M, N)
+    R.matmul_skinny(ref, x, w)
+    close(out, ref, 2e-2, 1e-2, "matmul_skinny")
+    # rows of a wider buffer (the decoder passes slices of padded buffers)
+    big_x = torch.zeros(16, K + 8, dtype=torch.bfloat16, device=DEV)
+    big_x[:M, :K] = x.to(DEV)
+    out2 = torch.zeros(16, N + 3, dtype=torch.bfloat16, device=DEV)
+    KN.matmul_skinny(out2[:M, :N], big_x[:M, :K], w.to(DEV))
+    assert torch.equal(out2[:M, :N], out) and float(out2[M:].abs().sum()) == 0 and float(out2[:, N:].abs().sum()) == 0
