@@ -140,12 +140,24 @@ def case(op):
         if op == "swiglu_fwd":
             return (lambda: K.swiglu_forward(h, x12)), 2.0 * 3 * N * H, 0.0
         return (lambda: K.swiglu_backward(dx12, dh, x12)), 2.0 * 5 * N * H, 0.0
+    if op in ("skinny_gemm", "skinny_gemm_wide"):
+        # a decoding step of LLaMA-3 8B: 4 rows against the fused MLP up-projection (235 MB of weights) or the QKV projection
+        Mr, Kd, Nw = 4, 4096, (28672 if op == "skinny_gemm" else 6144 * 8)
+        x, w = _bf(Mr, Kd), _bf(Nw, Kd, scale=0.02)
+        out = torch.empty(Mr, Nw, device=DEV, dtype=torch.bfloat16)
+        return (lambda: K.matmul_skinny(out, x, w)), 2.0 * (Nw * Kd + Mr * Kd + Mr * Nw), 2.0 * Mr * Nw * Kd
+    if op == "cached_attention":
+        # 32 rows decoding at position 4095 with 32 query heads over 8 cached heads of width 128 (537 MB of cache read)
+        B, Tmax, NH, NKV, HS = 32, 4096, 32, 8, 128
+        kc, vc = _bf(B, Tmax, NKV, HS), _bf(B, Tmax, NKV, HS)
+        q, out = _bf(B, NH * HS), torch.empty(B, NH * HS, device=DEV, dtype=torch.bfloat16)
+        return (lambda: K.cached_attention(out, q, kc, vc, 1, Tmax - 1, NH, NKV)), 2.0 * (kc.numel() + vc.numel()), 0.0
     raise SystemExit("unknown operator %r" % op)
 
 
 OPS = ["gemm_fwd", "gemm_gelu", "gemm_dgrad", "gemm_dgelu", "gemm_wgrad", "attn_fwd", "attn_bwd", "ln_fwd", "fused_residual", "ln_bwd", "ln_bwd_colsum",
        "classifier", "encoder_fwd", "encoder_bwd", "adamw", "norm", "bias_grad", "gelu", "rms_fwd", "rms_fused_residual", "rms_bwd", "rope_fwd",
-       "rope_bwd", "swiglu_fwd", "swiglu_bwd", "gemm_tf32", "gemm_fwd_1cta"]
+       "rope_bwd", "swiglu_fwd", "swiglu_bwd", "gemm_tf32", "gemm_fwd_1cta", "skinny_gemm", "skinny_gemm_wide", "cached_attention"]
 
 
 def main(argv):
