@@ -102,7 +102,8 @@ cached_attention_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
         for (int j = tid; j < cnt; j += DEC_THREADS) {
             const bf16* krow = kcache + ((b * Tmax + base + j) * NKV + g) * HS;
             float s = 0.f;
-            for (int p = 0; p < hp; p++) {
+            #pragma unroll 4
+            for (int p = 0; p < hp; p++) {                    // four independent 128-bit loads in flight per thread
                 const bf16x8 kk = ld128(krow + p * 8);
                 #pragma unroll
                 for (int e = 0; e < 8; e++) s += qs[p * 8 + e] * __bfloat162float(kk[e]);
@@ -124,6 +125,7 @@ cached_attention_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
         acc1 *= corr;
         m = m_new;
         if (my_group < groups) {
+            #pragma unroll 8
             for (int j = my_group; j < cnt; j += groups) {
                 const bf16* vrow = vcache + ((b * Tmax + base + j) * NKV + g) * HS;
                 const float2 vv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(vrow + 2 * my_pair));
@@ -148,67 +150,83 @@ cached_attention_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// Skinny product for decoding steps: out (M, N) = x (M, K) . w (N, K)^T with M <= 8 rows.  A 128-row tensor-core tile would
+// Skinny product for decoding steps: out (M, N) = x (M, K) . w (N, K)^T with M <= 8 rows.  A 128-row tcgen05 tile would
 // spend its time on padding and, worse, leave most SMs without a tile (N / 128 tiles for 148 SMs), while the step is bound by
-// streaming the weights once.  Here every warp owns SK_COLS output columns, its lanes stride over K with 128-bit streaming
-// loads (SK_UNROLL per column in flight), the few activation rows come through L1, and products accumulate in fp32.
-constexpr int SK_THREADS = 128;
-constexpr int SK_COLS = 2;
+// streaming the weights once.  Here a CTA owns 16 output columns and its 8 warps split K; a warp feeds warp-level
+// m16n8k16 MMAs with the weights as the 16-row operand and the (at most 8) activation rows as the 8-column operand, so that
+// the arithmetic costs two instructions per KB of weights and the loop is nothing but 128-bit streaming loads.  A lane
+// loads 8 consecutive K elements of weight rows g and g + 8 and of activation row g (g = lane / 4) and uses them as the
+// K slots of two MMAs; the dot product does not care that this permutes K, as long as both operands agree.
+constexpr int SK_WARPS = 8;
+constexpr int SK_THREADS = SK_WARPS * 32;
+constexpr int SK_COLS = 16;
 constexpr int SK_UNROLL = 4;
 constexpr int SK_MAX_M = 8;
 
-template <int MM>
+DEVINL void mma_16x8x16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
 __global__ void __launch_bounds__(SK_THREADS)
 skinny_gemm_kernel(bf16* __restrict__ out, const bf16* __restrict__ x, const bf16* __restrict__ w, int M, int N, int K,
                    int ldx, int ldw, int ldo) {
-    const int lane = threadIdx.x & 31;
-    const int warp = blockIdx.x * (SK_THREADS / 32) + (threadIdx.x >> 5);
-    const int n0 = warp * SK_COLS;
-    if (n0 >= N) return;
-    float acc[MM][SK_COLS];
-    #pragma unroll
-    for (int m = 0; m < MM; m++)
-        #pragma unroll
-        for (int c = 0; c < SK_COLS; c++) acc[m][c] = 0.f;
-    const bf16* wrow[SK_COLS];
-    #pragma unroll
-    for (int c = 0; c < SK_COLS; c++) wrow[c] = w + (size_t)min(n0 + c, N - 1) * ldw;      // a clamped column is computed, not stored
-    for (int kb = lane * 8; kb < K; kb += 32 * 8 * SK_UNROLL) {
-        bf16x8 wv[SK_UNROLL][SK_COLS];
+    __shared__ float red[SK_WARPS][4][32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int n0 = blockIdx.x * SK_COLS;
+    const bf16* w0 = w + (size_t)min(n0 + g, N - 1) * ldw;          // a clamped row is computed, not stored
+    const bf16* w1 = w + (size_t)min(n0 + g + 8, N - 1) * ldw;
+    const bool xvalid = g < M;
+    const bf16* xr = x + (size_t)min(g, M - 1) * ldx;
+    const int nchunks = (K + 31) >> 5;                               // 32 K elements per chunk: 8 per lane of a quad
+    const int per_warp = (nchunks + SK_WARPS - 1) / SK_WARPS;
+    const int c_begin = warp * per_warp, c_end = min(c_begin + per_warp, nchunks);
+    float c[4] = {0.f, 0.f, 0.f, 0.f};
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    // whole groups of SK_UNROLL full chunks: every load is issued before the first MMA, nothing is predicated
+    const int full_end = min(c_end, K >> 5);
+    int ch = c_begin;
+    for (; ch + SK_UNROLL <= full_end; ch += SK_UNROLL) {
+        uint4 a0[SK_UNROLL], a1[SK_UNROLL], b[SK_UNROLL];
         #pragma unroll
         for (int u = 0; u < SK_UNROLL; u++) {
-            const int k = kb + u * 256;
-            #pragma unroll
-            for (int c = 0; c < SK_COLS; c++) wv[u][c] = (k < K) ? ld128cs(wrow[c] + k) : bf16x8::zeros();
+            const int k = ((ch + u) << 5) + t * 8;
+            a0[u] = __ldcs(reinterpret_cast<const uint4*>(w0 + k));
+            a1[u] = __ldcs(reinterpret_cast<const uint4*>(w1 + k));
+            b[u] = *reinterpret_cast<const uint4*>(xr + k);
         }
         #pragma unroll
         for (int u = 0; u < SK_UNROLL; u++) {
-            const int k = kb + u * 256;
-            if (k >= K) break;
-            #pragma unroll
-            for (int m = 0; m < MM; m++) {
-                if (m < M) {
-                    const bf16x8 xv = ld128(x + (size_t)m * ldx + k);
-                    #pragma unroll
-                    for (int e = 0; e < 8; e++) {
-                        const float xe = __bfloat162float(xv[e]);
-                        #pragma unroll
-                        for (int c = 0; c < SK_COLS; c++) acc[m][c] += xe * __bfloat162float(wv[u][c][e]);
-                    }
-                }
-            }
+            if (!xvalid) b[u] = zero;
+            mma_16x8x16(c, a0[u].x, a1[u].x, a0[u].y, a1[u].y, b[u].x, b[u].y);
+            mma_16x8x16(c, a0[u].z, a1[u].z, a0[u].w, a1[u].w, b[u].z, b[u].w);
         }
     }
+    // the rest, one chunk at a time; the last chunk of K may be partial
+    for (; ch < c_end; ch++) {
+        const int k = (ch << 5) + t * 8;
+        const bool ok = k < K;
+        const uint4 a0 = ok ? __ldcs(reinterpret_cast<const uint4*>(w0 + k)) : zero;
+        const uint4 a1 = ok ? __ldcs(reinterpret_cast<const uint4*>(w1 + k)) : zero;
+        const uint4 b = (ok && xvalid) ? *reinterpret_cast<const uint4*>(xr + k) : zero;
+        mma_16x8x16(c, a0.x, a1.x, a0.y, a1.y, b.x, b.y);
+        mma_16x8x16(c, a0.z, a1.z, a0.w, a1.w, b.z, b.w);
+    }
     #pragma unroll
-    for (int m = 0; m < MM; m++)
+    for (int i = 0; i < 4; i++) red[warp][i][lane] = c[i];
+    __syncthreads();
+    if (warp == 0) {
+        // accumulator layout: c[2 i + j] = out[row 2 t + j][column n0 + g + 8 i]
         #pragma unroll
-        for (int c = 0; c < SK_COLS; c++) acc[m][c] = warp_sum(acc[m][c]);
-    if (lane == 0) {
-        #pragma unroll
-        for (int m = 0; m < MM; m++)
+        for (int i = 0; i < 4; i++) {
+            float v = 0.f;
             #pragma unroll
-            for (int c = 0; c < SK_COLS; c++)
-                if (m < M && n0 + c < N) out[(size_t)m * ldo + n0 + c] = __float2bfloat16_rn(acc[m][c]);
+            for (int ww = 0; ww < SK_WARPS; ww++) v += red[ww][i][lane];
+            const int m = 2 * t + (i & 1), n = n0 + g + 8 * (i >> 1);
+            if (m < M && n < N) out[(size_t)m * ldo + n] = __float2bfloat16_rn(v);
+        }
     }
 }
 
@@ -252,10 +270,8 @@ extern "C" int llmc_cached_attention(bf16* out, const bf16* q, const bf16* kcach
 // out (M, N) = x (M, K) . w (N, K)^T for M <= 8; K and the row strides of x and w are multiples of 8 elements.
 extern "C" int llmc_skinny_gemm(bf16* out, const bf16* x, const bf16* w, int M, int N, int K, int ldx, int ldw, int ldo, cudaStream_t stream) {
     if (M <= 0 || M > SK_MAX_M || N <= 0 || K <= 0 || (K % 8) || (ldx % 8) || (ldw % 8)) return -1;
-    const int warps = CEIL_DIV(N, SK_COLS);
-    const unsigned grid = (unsigned)CEIL_DIV(warps, SK_THREADS / 32);
-    if (M <= 4) skinny_gemm_kernel<4><<<grid, SK_THREADS, 0, stream>>>(out, x, w, M, N, K, ldx, ldw, ldo);
-    else skinny_gemm_kernel<8><<<grid, SK_THREADS, 0, stream>>>(out, x, w, M, N, K, ldx, ldw, ldo);
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return -1;
+    skinny_gemm_kernel<<<(unsigned)CEIL_DIV(N, SK_COLS), SK_THREADS, 0, stream>>>(out, x, w, M, N, K, ldx, ldw, ldo);
     CUDA_CHECK(cudaGetLastError());
     return 0;
 }
