@@ -31,6 +31,9 @@ class CachedDecoder:
         self.vcache = torch.zeros_like(self.kcache)
         self._rows = 0
         self._bufs = None
+        self._dense = None
+        # prompts of at least this many tokens per row, starting at position 0, run through the training attention kernel
+        self.dense_prefill_from = 128
         # steps of at most this many rows use the weight-streaming product instead of a padded tensor-core tile (0: never)
         self.skinny_rows = 8 if (model.device.type == "cuda" and model.dtype == torch.bfloat16) else 0
 
@@ -79,10 +82,26 @@ class CachedDecoder:
 
         ops.encoder_forward(x[:N].view(B, Tq, C), tokens, p["wte"], None)
         ops.rmsnorm_forward(ln[:N], rstd[:N], x[:N], p["ln1w"][0], eps)
+        # a long prompt from position 0 is the training forward pass: its attention kernel (tensor cores, one pass over the
+        # keys per 128 queries) replaces the per-query scan of the cache, and keys / values are copied into the cache afterwards
+        dense = pos is None and start_pos == 0 and Tq >= self.dense_prefill_from
+        if dense:
+            rep, HS = NH // NKV, cfg.head_size
+            if self._dense is None or self._dense[0].shape[0] < N or self._dense[1].numel() < B * NH * Tq:
+                self._dense = (torch.zeros(rows, 3 * C, dtype=m.dtype, device=m.device),
+                               torch.zeros(B * NH * Tq, dtype=torch.float32, device=m.device))
+            packed, lse = self._dense[0][:N], self._dense[1][:B * NH * Tq].view(B, NH, Tq)
         for l in range(L):
             mm(a["raw"], ln, p["qkvw"][l], N)
-            ops.rope_cache(a["q"][:N], self.kcache[l], self.vcache[l], a["raw"][:N], m.freqs, Tq, start_pos, NH, NKV, pos)
-            ops.cached_attention(a["atty"][:N], a["q"][:N], self.kcache[l], self.vcache[l], Tq, start_pos, NH, NKV, pos)
+            if dense:
+                ops.rope_forward(packed, a["raw"][:N], m.freqs, Tq, NH, NKV)
+                ops.attention_forward(a["atty"][:N], lse, packed, B, Tq, NH)
+                kv = packed.view(B, Tq, 3, NKV, rep, HS)
+                self.kcache[l][:B, :Tq].copy_(kv[:, :, 1, :, 0])
+                self.vcache[l][:B, :Tq].copy_(kv[:, :, 2, :, 0])
+            else:
+                ops.rope_cache(a["q"][:N], self.kcache[l], self.vcache[l], a["raw"][:N], m.freqs, Tq, start_pos, NH, NKV, pos)
+                ops.cached_attention(a["atty"][:N], a["q"][:N], self.kcache[l], self.vcache[l], Tq, start_pos, NH, NKV, pos)
             mm(a["proj"], a["atty"], p["attprojw"][l], N)
             ops.rmsnorm_fused_residual_forward(a["res"][:N], ln[:N], rstd[:N], x[:N], a["proj"][:N], p["ln2w"][l], eps)
             mm(a["fc12"], ln, p["fc12w"][l], N)

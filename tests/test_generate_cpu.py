@@ -34,6 +34,20 @@ def test_cached_logits_match_full_forward():
         assert torch.allclose(got, full[:, t], atol=1e-4, rtol=1e-4), "position %d" % t
 
 
+def test_dense_prefill_fills_the_cache_like_the_incremental_path():
+    m = small_model()
+    g = torch.Generator().manual_seed(1)
+    tok = torch.randint(0, m.cfg.vocab_size, (2, 24), generator=g, dtype=torch.int32)
+    a, b = G.CachedDecoder(m, 2, 32), G.CachedDecoder(m, 2, 32)
+    a.dense_prefill_from, b.dense_prefill_from = 8, 1000
+    la, lb = a.forward(tok[:, :20].contiguous(), 0), b.forward(tok[:, :20].contiguous(), 0)
+    assert torch.allclose(la, lb, atol=1e-5, rtol=1e-5)
+    assert torch.allclose(a.kcache, b.kcache, atol=1e-6) and torch.allclose(a.vcache, b.vcache, atol=1e-6)
+    for t in range(20, 24):
+        la, lb = a.forward(tok[:, t:t + 1].contiguous(), t), b.forward(tok[:, t:t + 1].contiguous(), t)
+    assert torch.allclose(la, lb, atol=1e-5, rtol=1e-5)
+
+
 def test_single_kv_head_and_full_heads():
     for desc in ("llama3:l=1,c=64,h=4,kv=1,t=32,v=50,m=16,f=1.0", "llama3:l=1,c=64,h=4,kv=4,t=32,v=50,m=16,f=1.3"):
         m = small_model(desc)

@@ -272,3 +272,24 @@ def test_skinny_product(M, N, K):
     out2 = torch.zeros(16, N + 3, dtype=torch.bfloat16, device=DEV)
     KN.matmul_skinny(out2[:M, :N], big_x[:M, :K], w.to(DEV))
     assert torch.equal(out2[:M, :N], out) and float(out2[M:].abs().sum()) == 0 and float(out2[:, N:].abs().sum()) == 0
+
+
+def test_long_prompt_through_the_training_attention_kernel():
+    """A prompt of 160 tokens per row takes the dense path (rotary + training attention kernel + cache copy); the same prompt
+    through the per-query cache scan must give the same cache and logits up to bf16 rounding, and decoding continues from it."""
+    from llmc_b200.models import generate as G
+    cfg = llama3.config_from_descriptor("llama3:l=2,c=256,h=4,kv=2,t=256,v=500,m=64,f=1.0")
+    m = llama3.Llama(cfg, DEV, torch.bfloat16, recompute=1)
+    m.init_random(9)
+    g = torch.Generator().manual_seed(0)
+    tok = torch.randint(0, cfg.vocab_size, (3, 170), generator=g, dtype=torch.int32).to(DEV)
+    dense, scan = G.CachedDecoder(m, 3, 192), G.CachedDecoder(m, 3, 192)
+    scan.dense_prefill_from = 10 ** 9
+    ld, ls = dense.forward(tok[:, :160].contiguous(), 0), scan.forward(tok[:, :160].contiguous(), 0)
+    assert dense._dense is not None and scan._dense is None
+    assert torch.equal(dense.kcache[0], scan.kcache[0]) and torch.equal(dense.vcache[0], scan.vcache[0])   # same rotation arithmetic
+    close(dense.kcache[1], scan.kcache[1], 3e-2, 3e-2, "keys of the second layer")
+    close(ld, ls, 3e-2, 3e-2, "prefill logits, dense vs scan")
+    for t in range(160, 170):
+        ld, ls = dense.forward(tok[:, t:t + 1].contiguous(), t), scan.forward(tok[:, t:t + 1].contiguous(), t)
+    close(ld, ls, 3e-2, 3e-2, "decode logits after dense prefill")
