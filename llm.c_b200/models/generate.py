@@ -186,6 +186,8 @@ def generate(model, prompt_tokens, max_gen_len, temperature=0.6, top_p=0.9, echo
             if graph_step is None:
                 graph_step = GraphStep(decoder, bsz, lo)
             logits = graph_step.step(step_in).cpu()
+            if int(graph_step.pos.item()) != cur:
+                raise RuntimeError("decoding graph is at position %d, expected %d" % (int(graph_step.pos.item()), cur))
         else:
             logits = decoder.forward(step_in, lo).cpu()
         if temperature > 0:

@@ -293,3 +293,23 @@ def test_long_prompt_through_the_training_attention_kernel():
     for t in range(160, 170):
         ld, ls = dense.forward(tok[:, t:t + 1].contiguous(), t), scan.forward(tok[:, t:t + 1].contiguous(), t)
     close(ld, ls, 3e-2, 3e-2, "decode logits after dense prefill")
+
+
+def test_trainer_samples_with_the_cache_during_training(tmp_path, capsys):
+    """The training loop of a LLaMA model on the GPU with validation and sampling switched on: sampling goes through the cached
+    decoder (graph-replayed steps) between optimizer steps and training continues afterwards."""
+    import numpy as np
+    from llmc_b200.train import TrainConfig, Trainer
+    from llmc_b200.utils.dataloader import write_datafile
+    rng = np.random.default_rng(0)
+    write_datafile(str(tmp_path / "train.bin"), rng.integers(0, 70000, size=40000), "llama-3")
+    write_datafile(str(tmp_path / "val.bin"), rng.integers(0, 70000, size=6000), "llama-3")
+    c = TrainConfig(train_data_pattern=str(tmp_path / "train.bin"), val_data_pattern=str(tmp_path / "val.bin"),
+                    load_filename="llama3:l=2,c=256,h=4,kv=2,t=128,v=70000,m=64,f=1.0", output_log_dir=str(tmp_path / "log"), B=2, T=128,
+                    total_batch_size=256, learning_rate=1e-3, weight_decay=0.1, val_loss_every=2, val_max_steps=2, sample_every=2, genT=12,
+                    max_steps=4, device="cuda", dtype="bf16", quiet=False, tokenizer_path=str(tmp_path / "none.bin"))
+    t = Trainer(c)
+    t.run()
+    t.close()
+    out = capsys.readouterr().out
+    assert out.count("generating:") >= 2 and "val loss" in out
