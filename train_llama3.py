@@ -11,6 +11,8 @@ initialisation; the Hugging Face id ``meta-llama/Meta-Llama-3.1-8B`` is accepted
 need a download, so they enter through a model file).  Token shards are the 32-bit files of the reference
 (magic 20240801).  ``--write_tensors 1`` writes the model file and the debug-state file (inputs, targets, logits, loss and
 all gradients of the first batch, fp32) that the reference script writes for cross-checking other implementations.
+``--inference_only 1`` reports the validation loss and generates from ``--prompt_tokens`` (batched prompts as token ids, key /
+value cache, nucleus sampling at ``--temperature`` / ``--top_p``; ``--use_kv 0`` recomputes the prefix instead).
 """
 import argparse
 import os
