@@ -141,17 +141,47 @@ class ClockSampler:
                 "reasons": sorted(reasons)}
 
 
-def write_shards(directory, ntok_train, ntok_val, seed):
+MAX_RANKS = 8     # shards are sized for the largest run of one node, whatever the world size of this run
+
+
+def shard_sizes(a):
+    """Token counts of the synthetic shards.  They depend on the batch geometry only, never on the world size, and are part
+    of the file names: a file left behind by a run with another geometry or rank count can neither be reused by mistake
+    nor be too small for a loader that wants world * B * T + 1 tokens (the reference's dataloader.h:186 asserts that)."""
+    ntok_train = max(2 * a.total_batch + 1, MAX_RANKS * a.batch * a.seq * 2 + 1, 4 * 1024 * 1024)
+    ntok_val = MAX_RANKS * a.batch * a.seq * 2 + 1
+    return ntok_train, ntok_val
+
+
+def write_shards(a, seed=1234):
+    """Writes (once) the train and validation shard of this geometry; returns (directory, train pattern, val pattern)."""
     from llmc_b200.utils.dataloader import write_synthetic_shard
+    ntok_train, ntok_val = shard_sizes(a)
+    directory = os.path.join(tempfile.gettempdir(), "llmc_b200_bench_data", "tr%d_va%d" % (ntok_train, ntok_val))
     os.makedirs(directory, exist_ok=True)
-    tr, va = os.path.join(directory, "synth_train_000000.bin"), os.path.join(directory, "synth_val_000000.bin")
-    if not os.path.exists(tr):
-        write_synthetic_shard(tr + ".tmp", ntok_train, 50257, seed)
-        os.replace(tr + ".tmp", tr)
-    if not os.path.exists(va):
-        write_synthetic_shard(va + ".tmp", ntok_val, 50257, seed + 1)
-        os.replace(va + ".tmp", va)
-    return tr, va
+    for name, ntok, sd in (("synth_train_000000.bin", ntok_train, seed), ("synth_val_000000.bin", ntok_val, seed + 1)):
+        path = os.path.join(directory, name)
+        want = 256 * 4 + 2 * ntok
+        if not os.path.exists(path) or os.path.getsize(path) != want:
+            tmp = "%s.tmp%d" % (path, os.getpid())
+            write_synthetic_shard(tmp, ntok, 50257, sd)
+            os.replace(tmp, path)
+    return directory
+
+
+def shard_patterns(a):
+    ntok_train, ntok_val = shard_sizes(a)
+    directory = os.path.join(tempfile.gettempdir(), "llmc_b200_bench_data", "tr%d_va%d" % (ntok_train, ntok_val))
+    return os.path.join(directory, "synth_train_*.bin"), os.path.join(directory, "synth_val_*.bin")
+
+
+def config_record(a, world, zero_stage):
+    """The workload description; both arms print exactly these keys so that their records can be compared field by field."""
+    return {"model": MODELS.get(a.model, a.model), "global_batch": a.total_batch, "micro_batch_per_gpu": a.batch, "seq_len": a.seq,
+            "grad_accum_steps": a.total_batch // (a.batch * a.seq * world),
+            "parallelism": ("dp%d-zero%d" % (world, zero_stage)) if world > 1 else "single", "recompute": a.recompute,
+            "optimizer": "AdamW fp32 master + stochastic rounding",
+            "l2": "no flush: every kernel's working set (activations 20+ GB per micro-step) exceeds the 126 MB L2"}
 
 
 def env_rank():
@@ -170,11 +200,9 @@ def run_ours(a):
         raise SystemExit("--gpus %d but WORLD_SIZE is %d: launch with torch.distributed.run" % (a.gpus, world))
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device")
-    data_dir = os.path.join(tempfile.gettempdir(), "llmc_b200_bench_data")
-    ntok = max(2 * a.total_batch + 1, 4 * 1024 * 1024)
     if rank == 0:
-        write_shards(data_dir, ntok, a.batch * a.seq * world * 2 + 1, 1234)
-    cfg = TrainConfig(train_data_pattern=os.path.join(data_dir, "synth_train_*.bin"), val_data_pattern="", load_filename=a.model,
+        write_shards(a)
+    cfg = TrainConfig(train_data_pattern=shard_patterns(a)[0], val_data_pattern="", load_filename=a.model,
                       B=a.batch, T=a.seq, total_batch_size=a.total_batch, learning_rate=6e-4, warmup_iterations=700,
                       final_learning_rate_frac=0.0, weight_decay=0.1, max_steps=10 ** 6, val_loss_every=0, sample_every=0,
                       recompute=a.recompute, zero_stage=a.zero, use_master_weights=1, comm_backend=a.comm, quiet=True)
@@ -203,8 +231,9 @@ def run_ours(a):
             model.targets.copy_(resident[micro][:, 1:])
             model.forward(model.inputs, model.targets, G, micro)
             model.backward(micro, last_micro_step=(micro == G - 1))
-        opt.grad_norm_sq()
+        opt.grad_norm_sq(model.acts["losses"], 1.0 / float(a.batch * a.seq * G))      # norm and loss, summed over the ranks
         opt.step(trainer.scheduler.get_learning_rate(step), cfg.weight_decay, step + 1)
+        opt.backend.end_step(updated=True)
 
     for s in range(a.warmup):
         device_step(s)
@@ -249,10 +278,8 @@ def run_ours(a):
             "metric": metric_name(a.model), "value": value, "unit": "tokens/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
             "ms_per_step": dev_ms / a.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": (value / PUBLISHED_BASELINE if a.model == "d12" else None),
             "dtype": "bf16", "data": "synthetic (seeded uniform-random uint16 tokens, random-init weights)",
-            "config": {"model": MODELS.get(a.model, a.model), "global_batch": a.total_batch, "micro_batch_per_gpu": a.batch, "seq_len": a.seq,
-                       "grad_accum_steps": G, "parallelism": ("dp%d-zero%d" % (world, opt.zero_stage)) if world > 1 else "single",
-                       "comm_backend": opt.backend.name, "recompute": a.recompute, "optimizer": "AdamW fp32 master + stochastic rounding",
-                       "l2": "no flush: every kernel's working set (activations 20+ GB per micro-step) exceeds the 126 MB L2"},
+            "config": config_record(a, world, opt.zero_stage),
+            "comm_backend": opt.backend.name,
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / a.steps,
                     "h2d_bytes_per_step": G * 2 * a.batch * a.seq * 4, "d2h_bytes_per_step": 8, "loss": last["loss"] if last else None},
@@ -278,11 +305,9 @@ def run_reference(a):
 
     if not os.path.exists(exe):
         return unavailable("baseline/_ref/train_gpt2cu is not built (see baseline/README.md)")
-    data_dir = os.path.join(tempfile.gettempdir(), "llmc_b200_bench_data")
-    ntok = max(2 * a.total_batch + 1, 4 * 1024 * 1024)
     sync_dir = os.path.join(tempfile.gettempdir(), "llmc_b200_ref_sync_%s" % os.environ.get("MASTER_PORT", "0"))
     if rank == 0:
-        write_shards(data_dir, ntok, a.batch * a.seq * world * 2 + 1, 1234)
+        write_shards(a)
         os.makedirs(sync_dir, exist_ok=True)
         stale = os.path.join(sync_dir, "ncclUniqueId.sync")
         if os.path.exists(stale):
@@ -294,7 +319,8 @@ def run_reference(a):
                 break
             time.sleep(0.1)
     total_steps = a.warmup + a.steps
-    cmd = [exe, "-i", os.path.join(data_dir, "synth_train_*.bin"), "-j", os.path.join(data_dir, "synth_val_*.bin"), "-e", a.model,
+    train_pattern, val_pattern = shard_patterns(a)
+    cmd = [exe, "-i", train_pattern, "-j", val_pattern, "-e", a.model,
            "-b", str(a.batch), "-t", str(a.seq), "-d", str(a.total_batch), "-z", str(a.zero), "-c", "0.1", "-l", "6e-4", "-u", "700", "-q", "0.0",
            "-r", str(a.recompute), "-x", str(total_steps), "-v", "1000000", "-m", "1", "-s", "1000000", "-g", "2", "-h", "0", "-n", "0"]
     # the reference's default rendezvous is MPI, which this build does not have: use its shared-file method at every N
@@ -336,9 +362,9 @@ def run_reference(a):
         "metric": metric_name(a.model), "value": value, "unit": "tokens/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms_per_step,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": (value / PUBLISHED_BASELINE if a.model == "d12" else None), "dtype": "bf16",
         "data": "synthetic (seeded uniform-random uint16 tokens, random-init weights)",
-        "config": {"model": MODELS.get(a.model, a.model), "global_batch": a.total_batch, "micro_batch_per_gpu": a.batch, "seq_len": a.seq,
-                   "parallelism": ("dp%d-zero%d" % (world, a.zero)) if world > 1 else "single", "recompute": a.recompute,
-                   "timing": "the reference's own per-step cudaEvent time (train_gpt2.cu:1827-1856), H2D of tokens and loss read-back included"},
+        "config": config_record(a, world, a.zero),
+        "comm_backend": "nccl",
+        "timing": "the reference's own per-step cudaEvent time (train_gpt2.cu:1827-1856), H2D of tokens and loss read-back included",
         "clocks": clocks,
         "e2e": {"value": value, "unit": "tokens/s", "ms_per_step": ms_per_step, "h2d_bytes_per_step": (a.total_batch // world) * 2 * 4,
                 "d2h_bytes_per_step": 8, "note": "the reference's step time already spans its H2D copies and loss read-back",

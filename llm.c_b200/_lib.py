@@ -79,6 +79,7 @@ def cuda():
         "llmc_bias_grad_scratch": (L, [I, I]),
         "llmc_bias_grad": (I, [P, P, P, I, I, I, S]),
         "llmc_norm_sq_scratch": (I, []),
+        "llmc_sum_f32": (I, [P, P, I, F, S]),
         "llmc_global_norm_sq": (I, [P, P, P, POINTER(TensorTable), S]),
         "llmc_adamw": (I, [P, P, P, P, P, POINTER(TensorTable), F, F, F, F, I, F, P, F, S]),
         "llmc_params_from_master": (I, [P, P, POINTER(TensorTable), S]),

@@ -51,6 +51,8 @@ __global__ void na_bias_grad_fold_kernel(bf16* __restrict__ dbias, const float* 
 
 // Device address of the scratch array, looked up once per device.  In host code the name
 // g_noalloc_scratch is only a handle for the runtime, not an address a kernel could use, hence the query.
+// The cache is filled without a lock: host threads that race on a device's first call all store the same
+// address, so the worst case is a repeated query.
 constexpr int NA_MAX_DEVICES = 64;
 float* g_scratch_addr[NA_MAX_DEVICES] = {nullptr};
 
@@ -78,6 +80,10 @@ extern "C" int llmc_bias_grad_noalloc(__nv_bfloat16* dbias, const __nv_bfloat16*
                                       cudaStream_t stream) {
     if (rows <= 0 || OC <= 0 || (OC % 8) != 0) {
         fprintf(stderr, "[llmc_b200] bias_grad_noalloc: need rows > 0 and OC a positive multiple of 8 (got rows %d, OC %d)\n", rows, OC);
+        return -1;
+    }
+    if (dbias == nullptr || dout == nullptr || (reinterpret_cast<uintptr_t>(dout) & 15u) != 0 || (reinterpret_cast<uintptr_t>(dbias) & 1u) != 0) {
+        fprintf(stderr, "[llmc_b200] bias_grad_noalloc: dout must be a non-null pointer aligned to 16 bytes and dbias a non-null bf16 pointer\n");
         return -1;
     }
     if (OC > LLMC_BIAS_GRAD_NOALLOC_MAX_FLOATS) {

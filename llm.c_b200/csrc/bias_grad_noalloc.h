@@ -21,8 +21,12 @@ extern "C" {
 
 // dbias[c] (+)= sum over r of dout[r, c]      (dout: rows x OC bf16 row-major, dbias: OC bf16)
 //
-// Returns 0 on success.  Returns -1 (and prints the reason to stderr) if OC is not a multiple of 8,
-// if rows or OC is not positive, or if the problem needs more scratch than the fixed array holds:
+// dout must be aligned to 16 bytes (the kernel reads it with 128-bit loads; with OC a multiple of 8 every row then is);
+// a view that starts at an odd offset of a larger tensor does not qualify.
+//
+// Returns 0 on success.  Returns -1 (and prints the reason to stderr) before any launch if OC is not a multiple of 8,
+// if rows or OC is not positive, if a pointer is null or dout is not aligned to 16 bytes, or if the problem needs
+// more scratch than the fixed array holds:
 // OC must not exceed LLMC_BIAS_GRAD_NOALLOC_MAX_FLOATS.  (Wider problems still run; fewer row strips
 // are used so that strips * OC fits the array.)  CUDA errors are returned as their cudaError_t value.
 //

@@ -14,6 +14,9 @@
 //                   of the reduced values (the global gradient norm needs no second pass).
 //                   Replaces ncclReduceScatter(ncclAvg) + global_norm_squared of the reference
 //                   (llmc/zero.cuh:539-548, train_gpt2.cu:1002-1023).
+//  all_reduce       the same kernel in its data-parallel (-z 0) form: the owner of a shard also stores the mean into every
+//                   peer's gradient buffer and, when its last CTA is done, raises a "broadcast done" flag on every peer;
+//                   the optimizer waits for all peers' flags.  Replaces ncclAllReduce(ncclAvg) (llmc/zero.cuh:532-538).
 //  scalar all-reduce one-shot: every rank stores {sequence, value} as one 64-bit word into its slot of
 //                   every peer's signal buffer and sums the N slots in rank order.
 //  adamw_allgather  AdamW + stochastic rounding on the own shards; each rounded bf16 pack is stored to
@@ -54,11 +57,13 @@ struct SliceList {
 #endif
 
 // signal buffer layout (64-bit words)
-constexpr int SIG_RS_BASE = 0;          // [channel 0..199][src rank]
+constexpr int SIG_RS_BASE = 0;          // [channel 0..199][src rank]  "my gradients of this group are final"
 constexpr int SIG_AG_BASE = 200 * MAX_RANKS;    // [channel 0..199][src rank]  "parameters of this group are published"
-constexpr int SIG_BARRIER = 400 * MAX_RANKS;
-constexpr int SIG_SCALAR = 401 * MAX_RANKS;     // [parity][src rank] packed {seq, float}
-constexpr int SIG_WORDS = 408 * MAX_RANKS;
+constexpr int SIG_AR_BASE = 400 * MAX_RANKS;    // [channel 0..199][src rank]  "my shard of this group's mean gradient is in your buffer"
+constexpr int SIG_BARRIER = 600 * MAX_RANKS;
+constexpr int SIG_SCALAR = 601 * MAX_RANKS;     // [parity][value 0..3][src rank] packed {seq, float}
+constexpr int MAX_SCALARS = 4;
+constexpr int SIG_WORDS = (601 + 2 * MAX_SCALARS) * MAX_RANKS;
 constexpr int MAX_CHANNELS = 200;
 
 // limit of every peer-flag wait in clock cycles; adjustable at run time (tests shorten it)
@@ -93,7 +98,8 @@ constexpr int RS_THREADS = 128;
 template <int THREADS>
 __global__ void __launch_bounds__(THREADS, THREADS == RS_THREADS ? 10 : 1)
 reduce_scatter_kernel(PeerPtrs grads, PeerPtrs sig, SliceList sl, int rank, int N, float scale, int channel,
-                      unsigned long long seq, float* __restrict__ norm_partials, int wait_peers, unsigned int* status) {
+                      unsigned long long seq, float* __restrict__ norm_partials, int wait_peers, int allreduce,
+                      unsigned int* __restrict__ done_counter, unsigned int* status) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     unsigned long long* my_sig = reinterpret_cast<unsigned long long*>(sig.p[rank]);
     // 1. tell every peer that this rank's gradients of `channel` are final (one warp of block 0)
@@ -145,42 +151,82 @@ reduce_scatter_kernel(PeerPtrs grads, PeerPtrs sig, SliceList sl, int rank, int 
                     const float f = __bfloat162float(o[e]);
                     acc_sq += f * f;
                 }
-                st128(mine + base + i * 8, o);
+                if (allreduce) {
+                    #pragma unroll
+                    for (int p = 0; p < MAX_RANKS; p++)
+                        if (p < N) st128(reinterpret_cast<bf16*>(grads.p[p]) + base + i * 8, o);      // own copy and every peer's
+                } else {
+                    st128(mine + base + i * 8, o);
+                }
             }
         }
     }
     // one partial sum of squares per warp (the host adds them all)
     acc_sq = warp_sum(acc_sq);
     if (lane == 0 && norm_partials) norm_partials[blockIdx.x * (THREADS / 32) + warp] = acc_sq;
+    if (allreduce) {
+        // the last CTA to get here tells every peer that this rank's shard of the channel has landed in its buffer
+        __threadfence_system();
+        const int last = __syncthreads_or(threadIdx.x == 0 && atomicAdd(done_counter, 1u) == gridDim.x - 1);
+        if (last) {
+            if (threadIdx.x == 0) *done_counter = 0;
+            if (threadIdx.x < N) {
+                __threadfence_system();
+                unsigned long long* peer = reinterpret_cast<unsigned long long*>(sig.p[threadIdx.x]);
+                st_release_sys(peer + SIG_AR_BASE + channel * MAX_RANKS + rank, seq);
+            }
+        }
+    }
 }
 
-__global__ void scalar_allreduce_kernel(PeerPtrs sig, float* __restrict__ inout, int rank, int N, unsigned long long seq,
-                                        unsigned int* status) {
-    __shared__ float vals[MAX_RANKS];
+// inout[v] = sum over ranks of inout[v], v < count <= MAX_SCALARS, summed in rank order (the same bits on every rank).  Before
+// the exchange, inout[0] may be replaced by the sum of `n_partials` partial sums (the squared-norm partials of the
+// reduce-scatter launches) and inout[1] by scale1 * sum of `n_terms` terms (the per-token losses): both sums use a fixed
+// tree, so the training loop needs no library reduction between backward and the update.
+__global__ void __launch_bounds__(256)
+scalar_allreduce_kernel(PeerPtrs sig, float* __restrict__ inout, int count, const float* __restrict__ partials, int n_partials,
+                        const float* __restrict__ terms, int n_terms, float scale1, int rank, int N, unsigned long long seq,
+                        unsigned int* status) {
+    __shared__ float red[32];
+    __shared__ float vals[MAX_SCALARS][MAX_RANKS];
     __shared__ int ok_s;
-    unsigned long long* my_sig = reinterpret_cast<unsigned long long*>(sig.p[rank]);
-    const int parity = (int)(seq & 1);
+    if (partials != nullptr) {
+        float acc = 0.f;
+        for (int i = threadIdx.x; i < n_partials; i += blockDim.x) acc += partials[i];
+        acc = block_sum(acc, red);
+        if (threadIdx.x == 0) inout[0] = acc;
+    }
+    if (terms != nullptr) {
+        float acc = 0.f;
+        for (int i = threadIdx.x; i < n_terms; i += blockDim.x) acc += terms[i];
+        acc = block_sum(acc, red);
+        if (threadIdx.x == 0) inout[1] = acc * scale1;
+    }
     if (threadIdx.x == 0) ok_s = 1;
     __syncthreads();
-    if (threadIdx.x < N) {
-        const unsigned long long word = (seq << 32) | (unsigned long long)__float_as_uint(inout[0]);
-        unsigned long long* peer = reinterpret_cast<unsigned long long*>(sig.p[threadIdx.x]);
-        st_release_sys(peer + SIG_SCALAR + parity * MAX_RANKS + rank, word);
-        // wait for slot threadIdx.x of my own buffer to carry this sequence number
-        const unsigned long long* slot = my_sig + SIG_SCALAR + parity * MAX_RANKS + threadIdx.x;
+    if (N == 1) return;
+    unsigned long long* my_sig = reinterpret_cast<unsigned long long*>(sig.p[rank]);
+    const int parity = (int)(seq & 1);
+    const int v = threadIdx.x / MAX_RANKS, p = threadIdx.x % MAX_RANKS;
+    if (v < count && p < N) {
+        const unsigned long long word = (seq << 32) | (unsigned long long)__float_as_uint(inout[v]);
+        unsigned long long* peer = reinterpret_cast<unsigned long long*>(sig.p[p]);
+        st_release_sys(peer + SIG_SCALAR + (parity * MAX_SCALARS + v) * MAX_RANKS + rank, word);
+        // wait for slot (v, p) of my own buffer to carry this sequence number
+        const unsigned long long* slot = my_sig + SIG_SCALAR + (parity * MAX_SCALARS + v) * MAX_RANKS + p;
         long long t0 = clock64();
         unsigned long long w;
         while (((w = ld_acquire_sys(slot)) >> 32) < (seq & 0xFFFFFFFFull)) {
-            if (clock64() - t0 > g_flag_wait_cycles) { record_error(status, ST_FLAG_TIMEOUT, 0x720 + threadIdx.x); ok_s = 0; break; }
+            if (clock64() - t0 > g_flag_wait_cycles) { record_error(status, ST_FLAG_TIMEOUT, 0x720 + p); ok_s = 0; break; }
             __nanosleep(100);
         }
-        vals[threadIdx.x] = __uint_as_float((unsigned int)(w & 0xFFFFFFFFull));
+        vals[v][p] = __uint_as_float((unsigned int)(w & 0xFFFFFFFFull));
     }
     __syncthreads();
-    if (threadIdx.x == 0 && ok_s) {
+    if (threadIdx.x < count && ok_s) {
         float s = 0.f;
-        for (int p = 0; p < N; p++) s += vals[p];
-        inout[0] = s;
+        for (int q = 0; q < N; q++) s += vals[threadIdx.x][q];
+        inout[threadIdx.x] = s;
     }
 }
 
@@ -259,9 +305,13 @@ adamw_allgather_kernel(PeerPtrs params, PeerPtrs sig, float* __restrict__ master
     }
 }
 
-__global__ void wait_flags_kernel(PeerPtrs sig, int rank, int N, int base, unsigned long long seq, unsigned int* status) {
+// waits for the N flags of each of `nch` consecutive channels starting at word `base`
+__global__ void wait_flags_kernel(PeerPtrs sig, int rank, int N, int base, int nch, unsigned long long seq, unsigned int* status) {
     const unsigned long long* my_sig = reinterpret_cast<const unsigned long long*>(sig.p[rank]);
-    if (threadIdx.x < N) wait_flag_ge(my_sig + base + threadIdx.x, seq, status, 0x740 + threadIdx.x);
+    const int p = threadIdx.x % MAX_RANKS;
+    if (p < N)
+        for (int ch = threadIdx.x / MAX_RANKS; ch < nch; ch += blockDim.x / MAX_RANKS)
+            if (!wait_flag_ge(my_sig + base + ch * MAX_RANKS + p, seq, status, 0x740 + p)) break;
 }
 
 __global__ void signal_flags_kernel(PeerPtrs sig, int rank, int N, int base, unsigned long long seq) {
@@ -304,13 +354,15 @@ static int rs_threads() {
 // Every slice size must be a multiple of 8*N. norm_partials: llmc_p2p_rs_partials(ctas) floats (may be null).
 extern "C" int llmc_p2p_reduce_scatter(const unsigned long long* grad_ptrs, const unsigned long long* sig_ptrs, const long long* offs,
                                        const long long* sizes, int count, int rank, int N, int channel, unsigned long long seq,
-                                       float* norm_partials, int ctas, int wait_peers, cudaStream_t stream) {
+                                       float* norm_partials, int ctas, int wait_peers, int allreduce, unsigned int* done_counter,
+                                       cudaStream_t stream) {
     PeerPtrs g, s; SliceList sl;
     if (fill(&g, grad_ptrs, N) || fill(&s, sig_ptrs, N) || count > 16 || channel < 0 || channel >= 200) return -1;
+    if (allreduce && done_counter == nullptr) return -1;
     sl.count = count;
     for (int i = 0; i < count; i++) { sl.off[i] = offs[i]; sl.size[i] = sizes[i]; if (sizes[i] % (8 * N) || offs[i] % 8) return -2; }
-    if (rs_threads() == 512) reduce_scatter_kernel<512><<<ctas, 512, 0, stream>>>(g, s, sl, rank, N, 1.0f / N, channel, seq, norm_partials, wait_peers, llmc_status_ptr());
-    else reduce_scatter_kernel<RS_THREADS><<<ctas, RS_THREADS, 0, stream>>>(g, s, sl, rank, N, 1.0f / N, channel, seq, norm_partials, wait_peers, llmc_status_ptr());
+    if (rs_threads() == 512) reduce_scatter_kernel<512><<<ctas, 512, 0, stream>>>(g, s, sl, rank, N, 1.0f / N, channel, seq, norm_partials, wait_peers, allreduce, done_counter, llmc_status_ptr());
+    else reduce_scatter_kernel<RS_THREADS><<<ctas, RS_THREADS, 0, stream>>>(g, s, sl, rank, N, 1.0f / N, channel, seq, norm_partials, wait_peers, allreduce, done_counter, llmc_status_ptr());
     CUDA_CHECK(cudaGetLastError());
     return 0;
 }
@@ -318,13 +370,21 @@ extern "C" int llmc_p2p_reduce_scatter(const unsigned long long* grad_ptrs, cons
 // number of partial sums of squares a reduce-scatter launch of `ctas` CTAs writes
 extern "C" int llmc_p2p_rs_partials(int ctas) { return ctas * (rs_threads() / 32); }
 
-extern "C" int llmc_p2p_allreduce_scalar(const unsigned long long* sig_ptrs, float* inout, int rank, int N, unsigned long long seq,
-                                         cudaStream_t stream) {
+// Sum of `count` (<= 4) device floats over the ranks, in place.  Optional fused local sums first: inout[0] = sum(partials),
+// inout[1] = scale1 * sum(terms).  A sequence number may be used once; consecutive calls use consecutive numbers.
+extern "C" int llmc_p2p_allreduce_scalars(const unsigned long long* sig_ptrs, float* inout, int count, const float* partials, int n_partials,
+                                          const float* terms, int n_terms, float scale1, int rank, int N, unsigned long long seq,
+                                          cudaStream_t stream) {
     PeerPtrs s;
-    if (fill(&s, sig_ptrs, N)) return -1;
-    scalar_allreduce_kernel<<<1, 32, 0, stream>>>(s, inout, rank, N, seq, llmc_status_ptr());
+    if (fill(&s, sig_ptrs, N) || count < 1 || count > MAX_SCALARS || (terms && count < 2)) return -1;
+    scalar_allreduce_kernel<<<1, 256, 0, stream>>>(s, inout, count, partials, n_partials, terms, n_terms, scale1, rank, N, seq, llmc_status_ptr());
     CUDA_CHECK(cudaGetLastError());
     return 0;
+}
+
+extern "C" int llmc_p2p_allreduce_scalar(const unsigned long long* sig_ptrs, float* inout, int rank, int N, unsigned long long seq,
+                                         cudaStream_t stream) {
+    return llmc_p2p_allreduce_scalars(sig_ptrs, inout, 1, nullptr, 0, nullptr, 0, 1.0f, rank, N, seq, stream);
 }
 
 extern "C" int llmc_p2p_adamw_allgather(const unsigned long long* param_ptrs, const unsigned long long* sig_ptrs, float* master,
@@ -346,13 +406,26 @@ extern "C" int llmc_p2p_adamw_allgather(const unsigned long long* param_ptrs, co
 // word offset, inside a rank's signal buffer, of the N "published" flags of a parameter group
 extern "C" int llmc_p2p_ag_flag_offset(int channel) { return SIG_AG_BASE + channel * MAX_RANKS; }
 
-// which: 0 = parameters of `channel` published (all-gather), 1 = barrier
+// which: 0 = parameters of `channel` published (all-gather), 1 = barrier, 2 = mean gradients of `channel` broadcast (all-reduce)
 extern "C" int llmc_p2p_wait(const unsigned long long* sig_ptrs, int rank, int N, int which, int channel, unsigned long long seq,
                              cudaStream_t stream) {
     PeerPtrs s;
     if (fill(&s, sig_ptrs, N)) return -1;
-    if (which == 0 && (channel < 0 || channel >= MAX_CHANNELS)) return -3;
-    wait_flags_kernel<<<1, 32, 0, stream>>>(s, rank, N, which == 0 ? SIG_AG_BASE + channel * MAX_RANKS : SIG_BARRIER, seq, llmc_status_ptr());
+    if (which != 1 && (channel < 0 || channel >= MAX_CHANNELS)) return -3;
+    const int base = which == 0 ? SIG_AG_BASE + channel * MAX_RANKS : which == 2 ? SIG_AR_BASE + channel * MAX_RANKS : SIG_BARRIER;
+    wait_flags_kernel<<<1, 32, 0, stream>>>(s, rank, N, base, 1, seq, llmc_status_ptr());
+    CUDA_CHECK(cudaGetLastError());
+    return 0;
+}
+
+// the same for `nch` consecutive channels in one launch (which: 0 or 2)
+extern "C" int llmc_p2p_wait_range(const unsigned long long* sig_ptrs, int rank, int N, int which, int channel0, int nch, unsigned long long seq,
+                                   cudaStream_t stream) {
+    PeerPtrs s;
+    if (fill(&s, sig_ptrs, N)) return -1;
+    if ((which != 0 && which != 2) || channel0 < 0 || nch < 1 || channel0 + nch > MAX_CHANNELS) return -3;
+    const int base = (which == 0 ? SIG_AG_BASE : SIG_AR_BASE) + channel0 * MAX_RANKS;
+    wait_flags_kernel<<<1, 256, 0, stream>>>(s, rank, N, base, nch, seq, llmc_status_ptr());
     CUDA_CHECK(cudaGetLastError());
     return 0;
 }
@@ -363,7 +436,7 @@ extern "C" int llmc_p2p_barrier(const unsigned long long* sig_ptrs, int rank, in
     if (fill(&s, sig_ptrs, N)) return -1;
     signal_flags_kernel<<<1, 32, 0, stream>>>(s, rank, N, SIG_BARRIER, seq);
     CUDA_CHECK(cudaGetLastError());
-    wait_flags_kernel<<<1, 32, 0, stream>>>(s, rank, N, SIG_BARRIER, seq, llmc_status_ptr());
+    wait_flags_kernel<<<1, 32, 0, stream>>>(s, rank, N, SIG_BARRIER, 1, seq, llmc_status_ptr());
     CUDA_CHECK(cudaGetLastError());
     return 0;
 }

@@ -63,13 +63,13 @@ norm_sq_kernel(float* __restrict__ partials, const bf16* __restrict__ grads, con
     if (threadIdx.x == 0) partials[blockIdx.y * gridDim.x + blockIdx.x] = acc;
 }
 
-// out[0] = sum(partials[0..n)) in index order with a fixed tree: deterministic
-__global__ void __launch_bounds__(1024) final_sum_kernel(float* __restrict__ out, const float* __restrict__ partials, int n) {
+// out[0] = scale * sum(partials[0..n)) in index order with a fixed tree: deterministic
+__global__ void __launch_bounds__(1024) final_sum_kernel(float* __restrict__ out, const float* __restrict__ partials, int n, float scale = 1.0f) {
     __shared__ float red[32];
     float acc = 0.f;
     for (int i = threadIdx.x; i < n; i += 1024) acc += partials[i];
     acc = block_sum(acc, red);
-    if (threadIdx.x == 0) out[0] = acc;
+    if (threadIdx.x == 0) out[0] = acc * scale;
 }
 
 DEVINL unsigned int sr_position(long long idx, int layer) {
@@ -187,6 +187,14 @@ to_master_kernel(float* __restrict__ master, const bf16* __restrict__ params, co
 int opt_grid_x() { int sms = llmc_device_sm_count(); if (sms <= 0) sms = 148; return sms; }
 
 }  // namespace
+
+// out[0] = scale * sum of n floats, one block, fixed summation tree (the mean loss of a step; reference:
+// global_sum_deterministic, llmc/cuda_utils.cuh:188-206)
+extern "C" int llmc_sum_f32(float* out, const float* in, int n, float scale, cudaStream_t stream) {
+    final_sum_kernel<<<1, 1024, 0, stream>>>(out, in, n, scale);
+    CUDA_CHECK(cudaGetLastError());
+    return 0;
+}
 
 extern "C" int llmc_norm_sq_scratch() { return 16 * opt_grid_x(); }
 

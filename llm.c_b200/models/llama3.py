@@ -298,7 +298,9 @@ class Llama:
 
     def loss(self, grad_accum_steps=1):
         B, T = self.act_shape
-        return self.acts["losses"].sum() / float(B * T * grad_accum_steps)
+        out = torch.empty(1, dtype=torch.float32, device=self.device)
+        ops.sum_scaled(out, self.acts["losses"], 1.0 / float(B * T * grad_accum_steps))
+        return out[0]
 
     def logits(self):
         B, T = self.act_shape

@@ -18,7 +18,7 @@ _NAMES = [
     "encoder_forward", "encoder_backward", "layernorm_forward", "fused_residual_forward", "layernorm_backward",
     "matmul_forward", "matmul_dgrad", "matmul_wgrad", "bias_grad", "attention_forward", "attention_backward",
     "fused_classifier", "gelu_forward", "gelu_backward_inplace", "residual_add", "global_norm_sq", "adamw_update",
-    "params_from_master", "master_from_params",
+    "params_from_master", "master_from_params", "sum_scaled",
     "rmsnorm_forward", "rmsnorm_fused_residual_forward", "rmsnorm_backward", "rope_forward", "rope_backward",
     "swiglu_forward", "swiglu_backward", "rope_cache", "cached_attention", "matmul_skinny",
 ]
@@ -26,15 +26,19 @@ _NAMES = [
 
 # operators whose first argument is an fp32 statistic or master copy in every mode: the second argument decides
 _DECIDED_BY_SECOND = {"global_norm_sq", "master_from_params"}
+# operators on fp32 statistics only: the device alone decides
+_DECIDED_BY_DEVICE = {"sum_scaled"}
 
 
 def _dispatch(name):
     k, r = getattr(kernels, name), getattr(reference, name)
     which = 1 if name in _DECIDED_BY_SECOND else 0
 
+    by_device = name in _DECIDED_BY_DEVICE
+
     def op(*args, **kwargs):
         t = args[which]
-        return (k if (t.is_cuda and t.dtype != torch.float32) else r)(*args, **kwargs)
+        return (k if (t.is_cuda and (by_device or t.dtype != torch.float32)) else r)(*args, **kwargs)
 
     op.__name__ = name
     op.__doc__ = k.__doc__

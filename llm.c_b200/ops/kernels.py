@@ -360,6 +360,13 @@ def global_norm_sq(out, grads, views):
     check(lib.llmc_global_norm_sq(_p(out), _p(part), _p(grads), ctypes.byref(tab), _stream()), "llmc_global_norm_sq")
 
 
+def sum_scaled(out, terms, scale=1.0):
+    """out[0] = scale * sum(terms) over fp32 device tensors, one block, fixed summation tree (the mean loss of a step)."""
+    global _launches
+    _launches += 1
+    check(_lib.cuda().llmc_sum_f32(_p(out), _p(terms), terms.numel(), float(scale), _stream()), "llmc_sum_f32")
+
+
 def adamw_update(params, master, grads, m, v, views, lr, beta1, beta2, eps, t, grad_scale=1.0, norm_sq=None, grad_clip=1.0):
     """AdamW on the views; bf16 params are stochastically rounded from the fp32 result."""
     global _launches

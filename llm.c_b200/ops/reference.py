@@ -226,6 +226,10 @@ def global_norm_sq(out, grads, views):
     out[0] = acc
 
 
+def sum_scaled(out, terms, scale=1.0):
+    out[0] = terms.sum() * scale
+
+
 def adamw_update(params, master, grads, m, v, views, lr, beta1, beta2, eps, t, grad_scale=1.0, norm_sq=None, grad_clip=1.0):
     """Round-to-nearest instead of stochastic rounding (the CPU path keeps fp32 parameters anyway)."""
     scale = grad_scale

@@ -3,12 +3,15 @@
 The flat parameter and gradient buffers and one small signal buffer are allocated as symmetric memory
 (``torch.distributed._symmetric_memory``: same size on every rank, every rank can address every peer's copy).
 NCCL is used only to rendezvous and to exchange the buffer handles.  After that a training step issues no NCCL
-call: the per-layer gradient reduce-scatter (fused with the 1/N scale and the norm^2 partial sums), the scalar
-all-reduce of the norm and the AdamW update fused with the all-gather of the rounded bf16 parameters are all
-kernels that load from / store to peer memory directly.
+call: the per-layer gradient reduce-scatter (fused with the 1/N scale and the norm^2 partial sums) or, without
+optimizer-state sharding (-z 0), the all-reduce form of the same kernel; the one-shot all-reduce that carries the
+squared norm and the loss together; the AdamW update fused with the all-gather of the rounded bf16 parameters;
+host scalars (validation loss, evaluation counts) and the barrier before a checkpoint's DONE marker are all kernels
+that load from / store to peer memory directly.
 
-Capability parity: multi_gpu_async_reduce_gradient, the ncclAllReduce of the norm and the ncclAllGather of
-gpt2_update in the reference (llmc/zero.cuh:528-551, train_gpt2.cu:1002-1030 and 1101-1120).
+Capability parity: multi_gpu_async_reduce_gradient, the ncclAllReduce calls of the loss and the norm, the
+ncclAllGather of gpt2_update, multi_gpu_cpu_float_sum and multi_gpu_barrier in the reference (llmc/zero.cuh:480-487,
+528-551 and 582-594, train_gpt2.cu:958, 1002-1030 and 1101-1120).
 """
 import ctypes
 import os
@@ -31,9 +34,13 @@ def _cfg_lib():
         P, I, LL, F, U = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_ulonglong
         lib.llmc_p2p_signal_words.restype = I
         lib.llmc_p2p_reduce_scatter.restype = I
-        lib.llmc_p2p_reduce_scatter.argtypes = [P, P, P, P, I, I, I, I, U, P, I, I, P]
+        lib.llmc_p2p_reduce_scatter.argtypes = [P, P, P, P, I, I, I, I, U, P, I, I, I, P, P]
         lib.llmc_p2p_allreduce_scalar.restype = I
         lib.llmc_p2p_allreduce_scalar.argtypes = [P, P, I, I, U, P]
+        lib.llmc_p2p_allreduce_scalars.restype = I
+        lib.llmc_p2p_allreduce_scalars.argtypes = [P, P, I, P, I, P, I, F, I, I, U, P]
+        lib.llmc_p2p_wait_range.restype = I
+        lib.llmc_p2p_wait_range.argtypes = [P, I, I, I, I, I, U, P]
         lib.llmc_p2p_adamw_allgather.restype = I
         lib.llmc_p2p_adamw_allgather.argtypes = [P, P, P, P, P, P, ctypes.POINTER(_lib.TensorTable), I, I, F, F, F, F, I, F, P, F, U, P, I, I, P]
         lib.llmc_p2p_wait.restype = I
@@ -112,8 +119,9 @@ class ParamSync:
 class P2PBackend:
     name = "p2p"
 
-    def __init__(self, model, dist_cfg, arena, params, grads):
+    def __init__(self, model, dist_cfg, arena, params, grads, zero_stage=1):
         self.cfg = dist_cfg
+        self.zero_stage = zero_stage
         self.N, self.r = dist_cfg.num_processes, dist_cfg.process_rank
         self.lib = _cfg_lib()
         self.model = model
@@ -132,7 +140,8 @@ class P2PBackend:
         self.rs_partials = self.lib.llmc_p2p_rs_partials(self.rs_ctas)
         self.num_channels = model.cfg.num_layers + 1
         self.norm_partials = torch.zeros(self.num_channels * self.rs_partials, dtype=torch.float32, device=dev)
-        self.done_counter = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.done_counter = torch.zeros(2, dtype=torch.int32, device=dev)      # [0] update + gather, [1] all-reduce (other stream)
+        self.host_scalar = torch.zeros(1, dtype=torch.float32, device=dev)
         self.seq = 0            # optimizer-step sequence number shared by all flags of a step
         self.scalar_seq = 0
         self.barrier_seq = 0
@@ -153,8 +162,10 @@ class P2PBackend:
         self.stream.wait_stream(torch.cuda.current_stream())
         kernels._launches += 1
         part = self.norm_partials[ch * self.rs_partials:(ch + 1) * self.rs_partials]
+        self._channels_this_step = max(getattr(self, "_channels_this_step", 0), ch + 1)
         check(self.lib.llmc_p2p_reduce_scatter(self.c_grads, self.c_sig, offs, sizes, len(slices), self.r, self.N, ch, self.seq,
-                                               ctypes.c_void_p(part.data_ptr()), self.rs_ctas, 1,
+                                               ctypes.c_void_p(part.data_ptr()), self.rs_ctas, 1, int(self.zero_stage == 0),
+                                               ctypes.c_void_p(self.done_counter.data_ptr() + 4),
                                                ctypes.c_void_p(self.stream.cuda_stream)), "llmc_p2p_reduce_scatter")
 
     def _channel_of(self, slices):
@@ -167,19 +178,48 @@ class P2PBackend:
         return self._chan_map[key]
 
     def finish_reduce(self):
-        torch.cuda.current_stream().wait_stream(self.stream)
+        cur = torch.cuda.current_stream()
+        cur.wait_stream(self.stream)
+        if self.zero_stage == 0 and self.reduced_this_step:
+            # data parallel without sharding: every peer's shard of the mean must have landed in this rank's buffer
+            kernels._launches += 1
+            check(self.lib.llmc_p2p_wait_range(self.c_sig, self.r, self.N, 2, 0, self._channels_this_step, self.seq,
+                                               ctypes.c_void_p(cur.cuda_stream)), "llmc_p2p_wait_range")
 
-    def fused_norm_sq(self, out):
-        """out[0] = sum over ranks of the sum of squares of the reduced shards (partials written by the reduce kernels)."""
-        torch.sum(self.norm_partials, dim=0, keepdim=True, out=out)
-        self.all_reduce_scalar_sum(out)
-
-    def all_reduce_scalar_sum(self, t):
+    def fused_norm_sq(self, scalars, losses=None, loss_scale=1.0):
+        """scalars[0] = sum over ranks of the sum of squares of the reduced shards (partials written by the reduce kernels);
+        with ``losses``, scalars[1] = sum over ranks of loss_scale * sum(losses).  One launch, one exchange."""
         self.scalar_seq += 1
         kernels._launches += 1
-        check(self.lib.llmc_p2p_allreduce_scalar(self.c_sig, ctypes.c_void_p(t.data_ptr()), self.r, self.N, self.scalar_seq,
-                                                 ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)), "llmc_p2p_allreduce_scalar")
+        count = 2 if (losses is not None or scalars.numel() >= 2) else 1
+        check(self.lib.llmc_p2p_allreduce_scalars(self.c_sig, kernels._p(scalars), count, kernels._p(self.norm_partials),
+                                                  self.norm_partials.numel(), kernels._p(losses), losses.numel() if losses is not None else 0,
+                                                  float(loss_scale), self.r, self.N, self.scalar_seq,
+                                                  ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)), "llmc_p2p_allreduce_scalars")
+
+    def all_reduce_scalar_sum(self, t):
+        """Sum over ranks, in place, of the first min(t.numel(), 4) floats of a device tensor."""
+        self.scalar_seq += 1
+        kernels._launches += 1
+        check(self.lib.llmc_p2p_allreduce_scalars(self.c_sig, kernels._p(t), min(t.numel(), 4), None, 0, None, 0, 1.0, self.r, self.N,
+                                                  self.scalar_seq, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)),
+              "llmc_p2p_allreduce_scalars")
         return t
+
+    def host_float_sum(self, value):
+        """Sum of a host float over all ranks (validation loss, evaluation counts; reference: multi_gpu_cpu_float_sum)."""
+        self.host_scalar.fill_(float(value))
+        self.all_reduce_scalar_sum(self.host_scalar)
+        return float(self.host_scalar.item())
+
+    def end_step(self, updated):
+        """Closes the bookkeeping of one optimizer step, whether or not the update ran.  The next step's reductions get a new
+        sequence number; after a skipped update a device-side barrier keeps every rank from overwriting gradients that a
+        slower peer's reduction kernels may still be reading."""
+        if self.reduced_this_step and not updated:
+            self.barrier()
+        self.reduced_this_step = False
+        self._channels_this_step = 0
 
     # ---- parameter groups of the fused update + all-gather, in the order the forward pass consumes them:
     #      group 0 = everything the forward pass touches before / outside the layer GEMMs (embeddings, final norm, LM head and the
@@ -212,17 +252,18 @@ class P2PBackend:
                                                     kernels._p(norm_sq), grad_clip, self.seq, kernels._p(self.done_counter), 4 * self.ctas, ch,
                                                     st), "llmc_p2p_adamw_allgather")
         self.published_seq = self.seq
-        self.reduced_this_step = False
 
     def wait_params(self, channel=None):
-        """Tiny wait kernel(s) on the current stream: all groups, or one (0 = shared group, 1 + l = layer l)."""
+        """Tiny wait kernel on the current stream: all groups, or one (0 = shared group, 1 + l = layer l)."""
         if self.published_seq == 0:
             return
         st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-        chans = range(self.model.cfg.num_layers + 1) if channel is None else [channel]
-        for ch in chans:
-            kernels._launches += 1
-            check(self.lib.llmc_p2p_wait(self.c_sig, self.r, self.N, 0, ch, self.published_seq, st), "llmc_p2p_wait")
+        kernels._launches += 1
+        if channel is None:
+            check(self.lib.llmc_p2p_wait_range(self.c_sig, self.r, self.N, 0, 0, self.model.cfg.num_layers + 1, self.published_seq, st),
+                  "llmc_p2p_wait_range")
+        else:
+            check(self.lib.llmc_p2p_wait(self.c_sig, self.r, self.N, 0, channel, self.published_seq, st), "llmc_p2p_wait")
 
     def flag_address(self, channel):
         return self.sig_ptrs[self.r] + 8 * self.lib.llmc_p2p_ag_flag_offset(channel)
@@ -231,15 +272,22 @@ class P2PBackend:
         raise RuntimeError("the P2P backend gathers inside adamw_allgather")
 
     def barrier(self):
+        """Device-side barrier on the current stream (reference: multi_gpu_barrier)."""
         self.barrier_seq += 1
+        kernels._launches += 2
         check(self.lib.llmc_p2p_barrier(self.c_sig, self.r, self.N, self.barrier_seq,
                                         ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)), "llmc_p2p_barrier")
+
+    def host_barrier(self):
+        """Barrier that the host also waits for (before a checkpoint's DONE marker is written)."""
+        self.barrier()
+        torch.cuda.current_stream().synchronize()
 
 
 def try_create(model_factory_args, dist_cfg, zero_stage, log=print):
     """Returns (arena, flat buffers) prerequisites for the P2P backend or None if symmetric memory is unavailable or the
-    configuration is not ZeRO-1 on <= 8 ranks of one node."""
-    if zero_stage != 1 or dist_cfg.num_processes > MAX_RANKS or dist_cfg.device.type != "cuda":
+    configuration is not data parallelism (with or without ZeRO-1) on <= 8 ranks of one node."""
+    if zero_stage not in (0, 1) or dist_cfg.num_processes > MAX_RANKS or dist_cfg.device.type != "cuda":
         return None
     try:
         return SymmetricArena(dist_cfg)

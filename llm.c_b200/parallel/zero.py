@@ -38,6 +38,15 @@ class SingleBackend:
     def all_gather_slices(self, params_flat, slices):
         pass
 
+    def host_float_sum(self, value):
+        return float(value)
+
+    def host_barrier(self):
+        pass
+
+    def end_step(self, updated):
+        pass
+
 
 class NcclBackend:
     """NCCL collectives on a side stream (the reference's scheme, llmc/zero.cuh:528-551)."""
@@ -87,6 +96,17 @@ class NcclBackend:
         dist.all_reduce(t, op=dist.ReduceOp.SUM)
         return t
 
+    def host_float_sum(self, value):
+        t = torch.tensor([float(value)], dtype=torch.float64, device=self.cfg.device)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return float(t.item())
+
+    def host_barrier(self):
+        dist.barrier()
+
+    def end_step(self, updated):
+        pass
+
     def all_gather_slices(self, params_flat, slices):
         for off, size in slices:
             full = params_flat[off:off + size]
@@ -119,6 +139,10 @@ class ShardedAdamW:
         self.use_master = use_master_weights and model.dtype != torch.float32
         self.beta1, self.beta2, self.eps, self.grad_clip = beta1, beta2, eps, grad_clip
         self.backend = backend if backend is not None else (SingleBackend() if self.N == 1 else NcclBackend(cfg, zero_stage))
+        if hasattr(self.backend, "zero_stage") and self.backend.zero_stage != zero_stage:
+            if getattr(self.backend, "name", "") == "p2p" and any(per % (self.N * 8) for _, _, per, _ in sizes):
+                raise ValueError("the in-kernel NVLink backend needs every parameter tensor divisible by 8 x number of processes; use -cb nccl")
+            self.backend.zero_stage = zero_stage
         div = self.N if self.sharded else 1
         self.shard_num_parameters = model.num_parameters // div
         dev = model.device
@@ -130,8 +154,12 @@ class ShardedAdamW:
         self.master, w_managed = zeros_device_or_managed(n, torch.float32, dev, "master weights") if self.use_master else (None, False)
         self.state_in_managed_memory = m_managed or v_managed or w_managed
         self.master_initialized = False
-        self.norm_sq = torch.zeros(1, dtype=torch.float32, device=dev)
-        self.sampler = Sampler(13371337 + self.r)          # stochastic-rounding seed stream
+        # [0] squared gradient norm, [1] mean loss of the step summed over ranks: reduced over the ranks together, read back together
+        self.scalars = torch.zeros(2, dtype=torch.float32, device=dev)
+        self.norm_sq = self.scalars[0:1]
+        # stochastic-rounding seed stream: per rank when every rank rounds its own shard (the reference's 13371337 + rank); the same
+        # on every rank when all of them update full replicas, so that the replicas stay bit-identical
+        self.sampler = Sampler(13371337 + (self.r if self.sharded else 0))
         self.rng_state_last_update = self.sampler.state.value
         # static part of the views
         self.base_views = []
@@ -162,16 +190,24 @@ class ShardedAdamW:
             out.append(v)
         return out
 
-    def grad_norm_sq(self):
-        """Device tensor holding the squared norm of the (reduced) gradient over all ranks."""
+    def grad_norm_sq(self, loss_terms=None, loss_scale=1.0):
+        """Device tensor holding the squared norm of the (reduced) gradient over all ranks.  With ``loss_terms`` (the per-token
+        losses of this rank), ``self.scalars[1]`` receives loss_scale * sum(loss_terms) summed over the ranks in the same
+        exchange (reference: the ncclAllReduce calls of train_gpt2.cu:958 and :1022), so that every rank sees the same loss."""
         if self.N > 1:
             self.backend.finish_reduce()
-        if self.sharded and hasattr(self.backend, "fused_norm_sq"):
-            self.backend.fused_norm_sq(self.norm_sq)       # partial sums were produced by the reduce-scatter kernels
+        if self.N > 1 and hasattr(self.backend, "fused_norm_sq"):
+            # partial sums of squares were produced by the reduction kernels; one launch sums them, sums the losses and exchanges both
+            self.backend.fused_norm_sq(self.scalars, loss_terms, loss_scale)
             return self.norm_sq
         ops.global_norm_sq(self.norm_sq, self.model.grads_flat, self.views())
-        if self.sharded:
-            self.backend.all_reduce_scalar_sum(self.norm_sq)
+        if loss_terms is not None:
+            ops.sum_scaled(self.scalars[1:2], loss_terms, loss_scale)
+        if self.N > 1:
+            if self.sharded:
+                self.backend.all_reduce_scalar_sum(self.scalars)
+            elif loss_terms is not None:
+                self.backend.all_reduce_scalar_sum(self.scalars[1:2])      # gradients are replicated: only the loss differs per rank
         return self.norm_sq
 
     def step(self, learning_rate, weight_decay, t, grad_scale=1.0, init_from_master_only=False):

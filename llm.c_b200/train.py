@@ -7,6 +7,7 @@ optimizer step or ``run()`` for the whole loop.  A step enqueues all micro-steps
 the clip and the AdamW update without waiting for the GPU, and reads loss and gradient norm back once at the end.
 """
 import glob as _glob
+import ctypes
 import math
 import os
 import sys
@@ -50,6 +51,7 @@ Options (same letters as the reference trainer):
   -pn <int> num processes  -pr <int> process rank  -pg <int> GPUs per node  -pi <str> init method mpi|tcp|fs  -ps <ip>  -pf <path>
 Extensions:  -dev cpu|cuda   -dt bf16|fp32   -cb nccl|p2p (communication backend of the multi-GPU step)
              -b2 <float> AdamW beta2 (0.95)   -gc <float> gradient clipping norm (1.0; 0 = off)   -hp / -tp HellaSwag / tokenizer paths
+             -fw <float> limit, in seconds, of a kernel's wait for a flag written by another GPU (0 = the library's default, about 10 s)
              -wd <float> watchdog: end the process (exit code 17) if no optimizer step completes within this many seconds (0 = off)
 """
 
@@ -102,6 +104,7 @@ class TrainConfig:
     prefetch: bool = True
     beta2: float = 0.95
     grad_clip: float = 1.0
+    flag_wait_s: float = 0.0      # > 0: limit of in-kernel waits for peer flags, in seconds
     watchdog_s: float = 0.0       # > 0: end the process if no optimizer step completes within this many seconds
 
 
@@ -119,6 +122,7 @@ _FLAGS = {
     "-sg": ("skip_update_gradz", float), "-dev": ("device", str), "-dt": ("dtype", str), "-cb": ("comm_backend", str),
     "-hp": ("hellaswag_path", str), "-tp": ("tokenizer_path", str), "-b2": ("beta2", float), "-gc": ("grad_clip", float),
     "-wd": ("watchdog_s", float),
+    "-fw": ("flag_wait_s", float),
 }
 
 
@@ -224,9 +228,13 @@ class Trainer:
         m.allocate_grads()
         if arena is not None:
             from .parallel import p2p
-            backend = p2p.P2PBackend(m, d, arena, sym_bufs["params"], sym_bufs["grads"])
+            backend = p2p.P2PBackend(m, d, arena, sym_bufs["params"], sym_bufs["grads"], zero_stage=(1 if c.zero_stage == 1 else 0))
         self.opt = ShardedAdamW(m, d, c.zero_stage, bool(c.use_master_weights), backend, beta2=c.beta2,
                                 grad_clip=(c.grad_clip if c.grad_clip > 0 else 1e30))
+        if c.flag_wait_s > 0 and self.device.type == "cuda":
+            # the limit is counted in SM clock cycles; 2 GHz is an upper bound of the clock, so the wait lasts at least flag_wait_s
+            from . import _lib
+            _lib.check(_lib.cuda().llmc_p2p_set_wait_cycles(ctypes.c_longlong(int(c.flag_wait_s * 2.0e9))), "llmc_p2p_set_wait_cycles")
         self.logger = Logger(c.output_log_dir, d.process_rank, self.resuming)
         self.tokenizer = Tokenizer(c.tokenizer_path)
         self.scheduler = LearningRateScheduler(c.lr_scheduler_type, c.learning_rate, c.warmup_iterations, self.train_num_batches,
@@ -308,7 +316,7 @@ class Trainer:
         checkpoint.write_state(state_path, num_processes=d.num_processes, process_rank=d.process_rank, use_master_weights=self.opt.use_master,
                                step=step, rng_state=self.opt.sampler.state.value, rng_state_last_update=self.opt.rng_state_last_update,
                                m=self.opt.m, v=self.opt.v, master=self.opt.master, loader=self.train_loader)
-        pdist.barrier(d)
+        self.opt.backend.host_barrier()             # every rank's state file is complete before the marker appears
         if d.is_main:
             open(done_path, "w").close()
 
@@ -337,7 +345,7 @@ class Trainer:
             m.forward(m.inputs, m.targets, 1, 0, write_dlogits=False)
             total += m.loss(1)
         val = float(total.item()) / max(self.val_num_batches, 1)
-        return pdist.host_float_sum(self.dist, val) / self.dist.num_processes
+        return self.opt.backend.host_float_sum(val) / self.dist.num_processes
 
     def hellaswag(self):
         m, el = self.model, self.eval_loader
@@ -348,7 +356,7 @@ class Trainer:
             self._upload(inputs, targets)
             m.forward(m.inputs, m.targets, 1, 0, write_dlogits=False)
             correct += el.stat_losses(m.acts["losses"].view(self.cfg.B, self.cfg.T))
-        total = pdist.host_float_sum(self.dist, correct)
+        total = self.opt.backend.host_float_sum(correct)
         return total / el.num_examples
 
     def sample(self, genT):
@@ -399,14 +407,22 @@ class Trainer:
                 self._have_batch = True
             m.forward(m.inputs, m.targets, G, micro)
             m.backward(micro, last_micro_step=(micro == G - 1))
-        loss_dev = m.loss(G)
-        norm_sq = opt.grad_norm_sq()
+        # the squared gradient norm and the mean loss are summed over the ranks in one exchange and read back in one copy; every
+        # rank sees the same two numbers, so every rank takes the same decision about skipping the update
+        B_, T_ = m.act_shape
+        opt.grad_norm_sq(m.acts["losses"], 1.0 / float(B_ * T_ * G))
         lr = self.scheduler.get_learning_rate(step)
+        nproc = self.dist.num_processes
+
+        def read_back():
+            vals = opt.scalars.cpu()                                              # the single synchronisation of the step
+            nsq = float(vals[0])
+            return float(vals[1]) / nproc, (math.sqrt(max(nsq, 0.0)) if math.isfinite(nsq) else float("nan"))
+
         need_host_decision = c.skip_update_lossz != 0.0 or c.skip_update_gradz != 0.0
         skipped = False
         if need_host_decision:
-            vals = torch.cat([loss_dev.view(1), norm_sq.view(1)]).cpu()
-            loss, gnorm = float(vals[0]), math.sqrt(max(float(vals[1]), 0.0))
+            loss, gnorm = read_back()
             zl, zg = self.loss_detector.update(loss), self.norm_detector.update(gnorm)
             if math.isfinite(zl) and c.skip_update_lossz != 0.0 and zl > c.skip_update_lossz:
                 self.print0("skipping update due to loss z-score of %f" % zl)
@@ -418,11 +434,9 @@ class Trainer:
                 opt.step(lr, c.weight_decay, step + 1)
         else:
             opt.step(lr, c.weight_decay, step + 1)
-            vals = torch.cat([loss_dev.view(1), norm_sq.view(1)]).cpu()          # the single synchronisation of the step
-            loss, gnorm = float(vals[0]), math.sqrt(max(float(vals[1]), 0.0)) if math.isfinite(float(vals[1])) else float("nan")
+            loss, gnorm = read_back()
             zl, zg = self.loss_detector.update(loss), self.norm_detector.update(gnorm)
-        if self.dist.num_processes > 1:
-            loss = pdist.host_float_sum(self.dist, loss) / self.dist.num_processes
+        opt.backend.end_step(updated=not skipped)
         if self.device.type == "cuda":
             # a kernel that gave up a bounded wait (peer flag, mbarrier) left its reason in the status word; the device is
             # idle here (the loss was just read back), so reading it costs one small copy
@@ -441,16 +455,25 @@ class Trainer:
         c, d = self.cfg, self.dist
         p = self.print0
         start_step = self.step
+        beat = (lambda phase: self.watchdog.beat(self.step, phase)) if (self.watchdog.timeout_s > 0 or self.watchdog.log_dir) else (lambda phase: None)
         for step in range(start_step, self.train_num_batches + 1):
             last_step = step == self.train_num_batches
+            # the first iteration of a resumed run does not rewrite the checkpoint it has just loaded: that one is complete and
+            # carries its DONE marker, and a kill during the rewrite would leave a marked but damaged checkpoint
+            # (reference: the `resuming == 0` guard of train_gpt2.cu:1799-1812)
+            just_resumed = self.resuming and step == start_step
             if self.val_loader is not None and c.val_loss_every > 0 and (step % c.val_loss_every == 0 or last_step):
+                beat("validation")
                 val_loss = self.validate()
                 p("val loss %f" % val_loss)
                 self.logger.log_val(step, val_loss)
             if self.eval_loader is not None and ((step > 0 and step % c.val_loss_every == 0) or last_step):
+                beat("evaluation")
                 acc = self.hellaswag()
                 p("HellaSwag: %.4f" % acc)
                 self.logger.log_eval(step, acc)
+            if c.sample_every > 0 and ((step > 0 and step % c.sample_every == 0) or last_step):
+                beat("sampling")                      # every rank: only rank 0 samples, the others wait for it in their next step
             if d.is_main and c.sample_every > 0 and ((step > 0 and step % c.sample_every == 0) or last_step):
                 toks = self.sample(c.genT)
                 p("generating:\n---")
@@ -459,8 +482,10 @@ class Trainer:
                 else:
                     p(" ".join(str(t) for t in toks))
                 p("---")
-            if c.output_log_dir and c.checkpoint_every > 0 and ((step > 0 and step % c.checkpoint_every == 0) or last_step):
+            if c.output_log_dir and c.checkpoint_every > 0 and not just_resumed and ((step > 0 and step % c.checkpoint_every == 0) or last_step):
+                beat("checkpoint")
                 self.write_checkpoint(step)
+                beat("checkpoint written")
                 step_delete = step - c.checkpoints_keep * c.checkpoint_every
                 if c.checkpoints_keep > 0 and step_delete > 0 and (c.major_checkpoint_every == 0 or step_delete % c.major_checkpoint_every != 0):
                     checkpoint.delete_checkpoint(c.output_log_dir, step_delete, d.process_rank)

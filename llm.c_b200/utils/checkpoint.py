@@ -30,6 +30,31 @@ MODEL_MAGIC, STATE_MAGIC, LLAMA_MAGIC = 20240326, 20240527, 20240803
 CHUNK_ELEMS = 16 * 1024 * 1024
 
 
+class _atomic_write:
+    """Opens ``path + '.tmp'`` for writing and renames it onto ``path`` when the block ends without an exception: a process killed
+    in the middle of a checkpoint leaves no truncated file under the final name (the restart loop would load it)."""
+
+    def __init__(self, path):
+        self.path, self.tmp, self.f = path, path + ".tmp", None
+
+    def __enter__(self):
+        self.f = open(self.tmp, "wb")
+        return self.f
+
+    def __exit__(self, exc_type, exc, tb):
+        self.f.flush()
+        os.fsync(self.f.fileno())
+        self.f.close()
+        if exc_type is None:
+            os.replace(self.tmp, self.path)
+        else:
+            try:
+                os.remove(self.tmp)
+            except OSError:
+                pass
+        return False
+
+
 def _stream_out(f, t):
     """Writes a (device or host) tensor to an open file in bounded chunks."""
     flat = t.reshape(-1)
@@ -61,7 +86,7 @@ def write_model(path, model):
     version = 5 if model.dtype == torch.bfloat16 else 3
     header[:8] = [MODEL_MAGIC, version, cfg.max_seq_len, cfg.vocab_size, cfg.num_layers, cfg.num_heads, cfg.channels,
                   cfg.padded_vocab_size]
-    with open(path, "wb") as f:
+    with _atomic_write(path) as f:
         f.write(header.tobytes())
         _stream_out(f, model.params_flat)
 
@@ -138,7 +163,7 @@ def _write_llama(path, model):
     header[17:23] = np.array([cfg.ffn_dim_multiplier, cfg.norm_eps, cfg.rope_theta], dtype=np.float64).view(np.int32)
     header[23] = cfg.padded_vocab_size
     Vp, V = cfg.padded_vocab_size, cfg.vocab_size
-    with open(path, "wb") as f:
+    with _atomic_write(path) as f:
         f.write(header.tobytes())
         for t in _llama_file_tensors(model):
             if t.shape[0] == Vp and t.dim() == 2 and Vp != V:
@@ -196,7 +221,7 @@ def write_state(path, *, num_processes, process_rank, use_master_weights, step, 
     struct.pack_into("<Q", hb, 22 * 4, rng_state_last_update & 0xFFFFFFFFFFFFFFFF)
     struct.pack_into("<Q", hb, 30 * 4, shard_idx)
     struct.pack_into("<Q", hb, 32 * 4, sample_idx)
-    with open(path, "wb") as f:
+    with _atomic_write(path) as f:
         f.write(bytes(hb))
         _stream_out(f, m)
         _stream_out(f, v)

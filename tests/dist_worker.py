@@ -31,6 +31,7 @@ def main():
     ap.add_argument("--out", required=True)
     ap.add_argument("--family", default="gpt2")        # gpt2 | llama3
     ap.add_argument("--fail-rank", type=int, default=-1)   # this rank raises before its second step (failure-detection test)
+    ap.add_argument("--skip-step", type=int, default=-1)   # every rank skips the update of this step (as the outlier detector would)
     a = ap.parse_args()
 
     d = pdist.init_distributed(device_type=a.device, timeout_s=20 if a.fail_rank >= 0 else 120)
@@ -56,7 +57,7 @@ def main():
     backend = None
     if arena is not None:
         from llmc_b200.parallel import p2p
-        backend = p2p.P2PBackend(model, d, arena, bufs["params"], bufs["grads"])
+        backend = p2p.P2PBackend(model, d, arena, bufs["params"], bufs["grads"], zero_stage=a.zero)
     opt = ShardedAdamW(model, d, a.zero, True, backend)
     B, T = 2, 64
     accum = a.slots // world
@@ -68,11 +69,12 @@ def main():
             x, y = batch_for(step, rank * accum + micro, B, T, cfg.vocab_size)
             model.forward(x.to(d.device), y.to(d.device), accum, micro)
             model.backward(micro, micro == accum - 1)
-        loss = float(model.loss(accum))
-        loss = pdist.host_float_sum(d, loss) / world
-        opt.grad_norm_sq()
-        opt.step(1e-3, 0.1, step + 1)
-        losses.append(loss)
+        # norm and loss are summed over the ranks in one exchange, as in the trainer's step
+        opt.grad_norm_sq(model.acts["losses"], 1.0 / float(B * T * accum))
+        if step != a.skip_step:
+            opt.step(1e-3, 0.1, step + 1)
+        opt.backend.end_step(updated=(step != a.skip_step))
+        losses.append(float(opt.scalars[1]) / world)
     if a.device == "cuda":
         from llmc_b200 import _lib
         status = _lib.read_status()

@@ -61,3 +61,16 @@ def test_rank_failure_ends_the_job_without_hanging(tmp_path):
     assert "injected failure" in r.stdout
     assert time.time() - t0 < 200
     assert not os.path.exists(out)
+
+
+def test_skipped_update_on_cpu_ranks(tmp_path):
+    """Every rank skips the same update (the decision is taken on the loss and norm summed over the ranks): the run continues
+    and equals the single-process run that skips the same step."""
+    single, multi = str(tmp_path / "single.pt"), str(tmp_path / "multi.pt")
+    common = ["--device", "cpu", "--slots", "2", "--steps", "4", "--skip-step", "1"]
+    r1 = launch(1, single, common + ["--zero", "0"], 0)
+    assert r1.returncode == 0, r1.stdout[-2000:]
+    r2 = launch(2, multi, common + ["--zero", "1"], 29535)
+    assert r2.returncode == 0, r2.stdout[-2000:]
+    a, b = torch.load(single), torch.load(multi)
+    assert max(abs(x - y) for x, y in zip(a["losses"], b["losses"])) < 1e-4

@@ -1,5 +1,6 @@
-"""ZeRO-1 on real GPUs: the in-kernel NVLink path (P2P reduce-scatter / fused AdamW + all-gather / one-shot scalar
-all-reduce) against the NCCL path and against a single-GPU run with gradient accumulation.  Needs two GPUs."""
+"""Data parallelism on real GPUs: the in-kernel NVLink path (P2P reduce-scatter or all-reduce / fused AdamW + all-gather /
+one-shot scalar all-reduce) against the NCCL path and against a single-GPU run with gradient accumulation, on 2, 4 and 8
+GPUs (each case is skipped where the machine has fewer)."""
 import os
 import subprocess
 import sys
@@ -23,9 +24,14 @@ def launch(world, out, extra, port, timeout=600, env_extra=None):
     return subprocess.run(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=timeout)
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_p2p_and_nccl_zero1_match_single_gpu(tmp_path):
-    world = 2
+def need(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs %d GPUs" % world)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_p2p_and_nccl_zero1_match_single_gpu(tmp_path, world):
+    need(world)
     single, nccl, p2p = (str(tmp_path / n) for n in ("single.pt", "nccl.pt", "p2p.pt"))
     r = launch(1, single, ["--device", "cuda", "--zero", "0", "--slots", str(world)], 0)
     assert r.returncode == 0, r.stdout[-3000:]
@@ -68,3 +74,37 @@ def test_llama_p2p_zero1_matches_single_gpu(tmp_path):
     assert p["backend"] == "p2p" and p["zero"] == 1
     assert max(abs(x - y) for x, y in zip(s["losses"], p["losses"])) < 3e-2, (s["losses"], p["losses"])
     assert (s["params"] - p["params"]).abs().max().item() < 2e-2
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_p2p_allreduce_without_sharding_matches_single_gpu(tmp_path, world):
+    """-z 0 on the in-kernel path: the reduction kernel stores the mean into every rank's gradient buffer (all-reduce) and every
+    rank updates a full replica."""
+    need(world)
+    single, p2p = str(tmp_path / "single.pt"), str(tmp_path / "p2p.pt")
+    r = launch(1, single, ["--device", "cuda", "--zero", "0", "--slots", str(world)], 0)
+    assert r.returncode == 0, r.stdout[-3000:]
+    r = launch(world, p2p, ["--device", "cuda", "--zero", "0", "--slots", str(world), "--backend", "p2p"], 29561)
+    assert r.returncode == 0, r.stdout[-3000:]
+    s, p = torch.load(single), torch.load(p2p)
+    assert p["backend"] == "p2p" and p["zero"] == 0
+    assert max(abs(x - y) for x, y in zip(s["losses"], p["losses"])) < 3e-2, (s["losses"], p["losses"])
+    assert (s["params"] - p["params"]).abs().max().item() < 2e-2
+
+
+def test_skipped_update_keeps_the_two_backends_in_step(tmp_path):
+    """A step whose update is skipped on the host (the outlier detector's decision) must leave the flag sequence numbers of the
+    in-kernel path consistent: the following steps still match the NCCL path."""
+    world = 2
+    need(world)
+    nccl, p2p = str(tmp_path / "nccl.pt"), str(tmp_path / "p2p.pt")
+    common = ["--device", "cuda", "--zero", "1", "--slots", str(world), "--steps", "5", "--skip-step", "2"]
+    r = launch(world, nccl, common + ["--backend", "nccl"], 29571)
+    assert r.returncode == 0, r.stdout[-3000:]
+    r = launch(world, p2p, common + ["--backend", "p2p"], 29572)
+    assert r.returncode == 0, r.stdout[-3000:]
+    n, p = torch.load(nccl), torch.load(p2p)
+    assert p["backend"] == "p2p"
+    assert max(abs(x - y) for x, y in zip(n["losses"], p["losses"])) < 2e-2, (n["losses"], p["losses"])
+    assert (n["params"] - p["params"]).abs().max().item() < 2e-2
+    assert n["losses"][3] == pytest.approx(n["losses"][2], abs=0.3)      # nothing moved between step 2 and 3 but the batch

@@ -55,4 +55,7 @@ def test_noalloc_bias_grad_rejects_oversize():
     x = torch.zeros(8, dtype=torch.bfloat16, device="cuda")
     assert fn(x.data_ptr(), x.data_ptr(), 1, (1 << 20) + 8, 0, stream) == -1      # wider than the built-in scratch
     assert fn(x.data_ptr(), x.data_ptr(), 1, 12, 0, stream) == -1                 # not a multiple of 8
+    wide = torch.zeros(64, dtype=torch.bfloat16, device="cuda")
+    assert fn(x.data_ptr(), wide.data_ptr() + 2, 1, 8, 0, stream) == -1           # dout not aligned to 16 bytes: refused before any launch
+    assert fn(x.data_ptr(), None, 1, 8, 0, stream) == -1                          # null pointer
     torch.cuda.synchronize()
