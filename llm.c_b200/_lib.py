@@ -86,6 +86,7 @@ def cuda():
         "llmc_master_from_params": (I, [P, P, POINTER(TensorTable), S]),
         "llmc_attention_fwd": (I, [P, P, P, I, I, I, I, S]),
         "llmc_attention_bwd": (I, [P, P, P, P, P, P, I, I, I, I, S]),
+        "llmc_attention_bwd_workspace": (L, [I, I, I, I]),
     }
     for name, (res, args) in sigs.items():
         if hasattr(lib, name):

@@ -420,9 +420,18 @@ int launch_bwd(const CUtensorMap& tmQKV, const CUtensorMap& tmDO, const BwdArgs&
     return 0;
 }
 
+// delta[b,h,t] = sum_d O[b,t,h,d] * dO[b,t,h,d] (shared with the single-pass kernel of attention_bwd1.cu)
+int llmc_attention_delta(float* delta, const bf16* out, const bf16* dout, int B, int T, int NH, int hs, cudaStream_t stream) {
+    const long long rows = (long long)B * T * NH;
+    delta_kernel<<<(unsigned)CEIL_DIV(rows * 8, 256), 256, 0, stream>>>(delta, out, dout, B, T, NH, hs);
+    CUDA_CHECK(cudaGetLastError());
+    return 0;
+}
+
 // dqkv (B,T,3,NH,HS) = gradient of causal attention; delta: scratch of B*NH*T floats.  Head sizes: multiples of 8, 64..128.
-extern "C" int llmc_attention_bwd(bf16* dqkv, float* delta, const bf16* dout, const bf16* qkv, const bf16* out, const float* lse,
-                                  int B, int T, int NH, int hs, cudaStream_t stream) {
+// The entry point llmc_attention_bwd (attention_bwd1.cu) sends every head size but 64 here.
+int llmc_attention_bwd_two_pass(bf16* dqkv, float* delta, const bf16* dout, const bf16* qkv, const bf16* out, const float* lse,
+                                int B, int T, int NH, int hs, cudaStream_t stream) {
     if (hs < 64 || hs > 128 || (hs % 8)) { fprintf(stderr, "[llmc_b200] attention backward: head size %d not supported (multiples of 8 from 64 to 128)\n", hs); return -1; }
     CUtensorMap tmQKV, tmDO;
     int rc = llmc_attn_qkv_map(&tmQKV, qkv, B, T, NH, hs);
@@ -433,9 +442,7 @@ extern "C" int llmc_attention_bwd(bf16* dqkv, float* delta, const bf16* dout, co
         uint32_t box[4] = {64, 1, 128, 1};
         if ((rc = llmc_get_tensormap(&tmDO, dout, 2, 4, dims, strides, box, 3))) return rc;
     }
-    const long long rows = (long long)B * T * NH;
-    delta_kernel<<<(unsigned)CEIL_DIV(rows * 8, 256), 256, 0, stream>>>(delta, out, dout, B, T, NH, hs);
-    CUDA_CHECK(cudaGetLastError());
+    if ((rc = llmc_attention_delta(delta, out, dout, B, T, NH, hs, stream))) return rc;
     BwdArgs a;
     a.dqkv = dqkv; a.lse = lse; a.delta = delta; a.B = B; a.T = T; a.NH = NH; a.hs = hs;
     a.scale = 1.0f / sqrtf((float)hs);

@@ -155,6 +155,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN, B_MN);
+            constexpr uint32_t A_STEP = A_MN == 0 ? UMMA_K * 2 : UMMA_K * 128;      // bytes per K step of 16 inside a stage
+            constexpr uint32_t B_STEP = B_MN == 0 ? UMMA_K * 2 : UMMA_K * 128;
+            const uint64_t da0 = A_MN == 0 ? umma_desc_sw128(smem_u32(smem), 16, 1024) : umma_desc_sw128(smem_u32(smem), BK * 128, 1024);
+            const uint64_t db0 = B_MN == 0 ? umma_desc_sw128(smem_u32(smem) + A_STAGE_BYTES, 16, 1024)
+                                           : umma_desc_sw128(smem_u32(smem) + A_STAGE_BYTES, BK * 128, 1024);
             int stage = 0; uint32_t phase = 0;
             int it = 0;
             for (int w = blockIdx.x; w < total_work; w += gridDim.x, it++) {
@@ -168,17 +173,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 for (int kb = kb0; kb < kb1; kb++) {
                     if (!mbar_wait(&full[stage], phase, abort_flag, g.status, 0x300 + stage)) break;
                     tc_fence_after();
-                    const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
-                    const uint32_t sb = sa + A_STAGE_BYTES;
+                    // descriptors of this stage = those of stage 0 plus the stage offset (the start address sits in the low bits of
+                    // a descriptor, in 16-byte units): per instruction the issuing thread does two additions, not two constructions
+                    const uint64_t da_s = da0 + (uint64_t)(stage * (STAGE_BYTES >> 4));
+                    const uint64_t db_s = db0 + (uint64_t)(stage * (STAGE_BYTES >> 4));
                     #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; k++) {
-                        uint64_t da, db;
-                        if (A_MN == 0) da = umma_desc_sw128(sa + k * (UMMA_K * 2), 16, 1024);
-                        else           da = umma_desc_sw128(sa + k * (UMMA_K * 128), BK * 128, 1024);
-                        if (B_MN == 0) db = umma_desc_sw128(sb + k * (UMMA_K * 2), 16, 1024);
-                        else           db = umma_desc_sw128(sb + k * (UMMA_K * 128), BK * 128, 1024);
-                        umma_ss(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
-                    }
+                    for (int k = 0; k < BK / UMMA_K; k++)
+                        umma_ss(d_tmem, da_s + k * (A_STEP >> 4), db_s + k * (B_STEP >> 4), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
                     umma_commit(&empty[stage]);      // frees the smem stage once these MMAs have read it
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }

@@ -211,6 +211,11 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         // ---------------- MMA issuer (leader CTA only) ----------------
         if (lane == 0 && rank == 0) {
             constexpr uint32_t idesc = umma_idesc_bf16(256, BN, A_MN, B_MN);
+            constexpr uint32_t A_STEP = A_MN == 0 ? UMMA_K * 2 : UMMA_K * 128;      // bytes per K step of 16 inside a stage
+            constexpr uint32_t B_STEP = B_MN == 0 ? UMMA_K * 2 : UMMA_K * 128;
+            const uint64_t da0 = A_MN == 0 ? umma_desc_sw128(smem_u32(smem), 16, 1024) : umma_desc_sw128(smem_u32(smem), BK * 128, 1024);
+            const uint64_t db0 = B_MN == 0 ? umma_desc_sw128(smem_u32(smem) + A_STAGE_BYTES, 16, 1024)
+                                           : umma_desc_sw128(smem_u32(smem) + A_STAGE_BYTES, BK * 128, 1024);
             int stage = 0; uint32_t phase = 0;
             int it = 0;
             for (int w = pair; w < total_work; w += npairs, it++) {
@@ -225,16 +230,14 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
                 for (int kb = kb0; kb < kb1; kb++) {
                     if (!mbar_wait(&full[stage], phase, abort_flag, g.status, 0xB00 + stage)) { fail = true; break; }
                     tc_fence_after();
-                    const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
-                    const uint32_t sb = sa + A_STAGE_BYTES;
+                    // descriptors of this stage = those of stage 0 plus the stage offset (the start address sits in the low bits of
+                    // a descriptor, in 16-byte units): an instruction costs its issuing thread two additions instead of two
+                    // descriptor constructions, which took longer than the product itself runs
+                    const uint64_t da_s = da0 + (uint64_t)(stage * (STAGE_BYTES >> 4));
+                    const uint64_t db_s = db0 + (uint64_t)(stage * (STAGE_BYTES >> 4));
                     #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; k++) {
-                        const uint64_t da = A_MN == 0 ? umma_desc_sw128(sa + k * (UMMA_K * 2), 16, 1024)
-                                                      : umma_desc_sw128(sa + k * (UMMA_K * 128), BK * 128, 1024);
-                        const uint64_t db = B_MN == 0 ? umma_desc_sw128(sb + k * (UMMA_K * 2), 16, 1024)
-                                                      : umma_desc_sw128(sb + k * (UMMA_K * 128), BK * 128, 1024);
-                        umma_ss_2sm(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
-                    }
+                    for (int k = 0; k < BK / UMMA_K; k++)
+                        umma_ss_2sm(d_tmem, da_s + k * (A_STEP >> 4), db_s + k * (B_STEP >> 4), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
                     umma_commit_2sm(&empty[stage]);      // frees this stage in both CTAs
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }

@@ -208,9 +208,11 @@ def attention_backward(dqkv, dout, qkv, out, lse, B, T, NH):
     """dqkv (B,T,3,NH,HS) from dout, the forward inputs and statistics; deterministic."""
     global _launches
     hs = qkv.numel() // (B * T * 3 * NH)
-    delta = _scratch.get("attn_delta", B * NH * T, torch.float32, qkv.device)
+    lib = _lib.cuda()
+    # row statistics and, for 64-wide heads, the per-pair dQ contributions of the single-pass kernel (csrc/attention_bwd1.cu)
+    ws = _scratch.get("attn_bwd", lib.llmc_attention_bwd_workspace(B, T, NH, hs), torch.float32, qkv.device)
     _launches += 3
-    check(_lib.cuda().llmc_attention_bwd(_p(dqkv), _p(delta), _p(dout), _p(qkv), _p(out), _p(lse), B, T, NH, hs, _stream()),
+    check(lib.llmc_attention_bwd(_p(dqkv), _p(ws), _p(dout), _p(qkv), _p(out), _p(lse), B, T, NH, hs, _stream()),
           "llmc_attention_bwd")
 
 

@@ -63,7 +63,7 @@ def case(op):
         causal = 4.0 * B * NH * T * T * 64 / 2
         if op == "attn_fwd":
             return (lambda: K.attention_forward(out, lse, qkv, B, T, NH)), 2.0 * (qkv.numel() + out.numel()), causal
-        return (lambda: K.attention_backward(dqkv, dout, qkv, out, lse, B, T, NH)), 2.0 * (2 * qkv.numel() + 2 * out.numel()), 3.5 * causal
+        return (lambda: K.attention_backward(dqkv, dout, qkv, out, lse, B, T, NH)), 2.0 * (2 * qkv.numel() + 2 * out.numel()), 2.5 * causal      # five products per tile pair
     if op in ("ln_fwd", "fused_residual", "ln_bwd", "ln_bwd_colsum"):
         N = 65536
         x, y, w, b, dy = _bf(N, C), _bf(N, C), _bf(C) + 1, _bf(C), _bf(N, C)
