@@ -175,14 +175,14 @@ attn_bwd1_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
             for (; wk.valid(); wk.next()) {
                 if (wk.first_of_tile()) {
                     const int rb = kvt & 1;
-                    if (!mbar_wait(&res_empty[rb], ((kvt >> 1) & 1) ^ 1, abort_flag, a.status, 0x681)) break;
+                    if (!mbar_wait_relaxed(&res_empty[rb], ((kvt >> 1) & 1) ^ 1, abort_flag, a.status, 0x681)) break;
                     uint8_t* rdst = sRes + rb * PAIR_BYTES;
                     mbar_expect_tx(&res_full[rb], PAIR_BYTES);
                     tma_load_4d(rdst, &tmQKV, &res_full[rb], 0, a.NH + wk.h, wk.j * BT, wk.b);                    // K_j
                     tma_load_4d(rdst + TILE_BYTES, &tmQKV, &res_full[rb], 0, 2 * a.NH + wk.h, wk.j * BT, wk.b);   // V_j
                     kvt++;
                 }
-                if (!mbar_wait(&x_empty[xst], xph ^ 1, abort_flag, a.status, 0x680)) break;
+                if (!mbar_wait_relaxed(&x_empty[xst], xph ^ 1, abort_flag, a.status, 0x680)) break;
                 uint8_t* dst = sStr + xst * PAIR_BYTES;
                 mbar_expect_tx(&x_full[xst], PAIR_BYTES);
                 tma_load_4d(dst, &tmQKV, &x_full[xst], 0, wk.h, wk.i * BT, wk.b);                                 // Q_i
@@ -198,7 +198,7 @@ attn_bwd1_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
         // Wait results go through a warp vote so that the compiler knows the branches on them to be uniform.
         if (wk.valid()) {
             const bool leader = elect_one();
-#define WAIT_ALL(bar, parity, code) (__all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, a.status, code)) != 0)
+#define WAIT_ALL(bar, parity, code) (__all_sync(0xffffffffu, mbar_wait_relaxed(bar, parity, abort_flag, a.status, code, 32)) != 0)
             constexpr uint32_t idesc_s = umma_idesc_bf16(BT, BT, 0, 0);      // S^T, dP^T: both operands K-major
             constexpr uint32_t idesc_ts = umma_idesc_bf16(BT, HS, 0, 1);     // dV, dK: A from TMEM, B N-major
             constexpr uint32_t idesc_q = umma_idesc_bf16(BT, HS, 1, 1);      // dQ: A = dS^T read M-major, B = K_j N-major
@@ -315,37 +315,59 @@ attn_bwd1_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
             ok = mbar_wait(s_full, t & 1, abort_flag, a.status, 0x6a0) && ok;
             tc_fence_after();
             if (threadIdx.x == 128) TRACE(1, 1);
-            uint32_t sv[64];
-            tmem_ld32(tS + lane_off + hf * 64, sv);
-            tmem_ld32(tS + lane_off + hf * 64 + 32, sv + 32);
-            tmem_ld_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(s_empty);
             ok = mbar_wait(&st_full[t & 1], (t >> 1) & 1, abort_flag, a.status, 0x6a1) && ok;
-            // ---- P^T = exp2(S^T * scale * log2(e) - LSE * log2(e)); causal: query >= key
+            if (t > 0) ok = mbar_wait(p_empty, (t - 1) & 1, abort_flag, a.status, 0x6a2) && ok;      // dV(t-1) has read P^T(t-1)
+            if (threadIdx.x == 128) TRACE(1, 7);
+            // ---- P^T = exp2(S^T * scale * log2(e) - LSE * log2(e)); causal: query >= key.  Two passes of 32 queries: with all 64
+            //      scores in registers next to the 64 results the register file is so full that the compiler reuses registers
+            //      across the exponentials, and every one then waits for its predecessor (measured: 34 cycles per element).
             float p[64];
-            const bool diag = (i == j);
+            // only the diagonal tile and a ragged last key tile need masks; both conditions are the same for the whole warp
+            const bool masked = (i == j) || (j * BT + BT > a.T);
             #pragma unroll
-            for (int e4 = 0; e4 < 16; e4++) {
-                const float4 l4 = *reinterpret_cast<const float4*>(stat + e4 * 4);
-                const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
-                #pragma unroll
-                for (int k = 0; k < 4; k++) {
-                    const int e = e4 * 4 + k;
-                    float v = ex2_fast(fmaf(__uint_as_float(sv[e]), a.scale_log2e, -lv[k]));
-                    if (diag && hf * 64 + e < r) v = 0.f;
-                    p[e] = row_ok ? v : 0.f;
+            for (int h2 = 0; h2 < 2; h2++) {
+                uint32_t sv[32];
+                tmem_ld32(tS + lane_off + hf * 64 + h2 * 32, sv);
+                tmem_ld_wait();
+                if (h2 == 1) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(s_empty);
+                    if (threadIdx.x == 128) TRACE(1, 6);
+                }
+                if (!masked) {
+                    #pragma unroll
+                    for (int e4 = 0; e4 < 8; e4++) {
+                        const float4 l4 = *reinterpret_cast<const float4*>(stat + h2 * 32 + e4 * 4);
+                        p[h2 * 32 + e4 * 4 + 0] = ex2_fast(fmaf(__uint_as_float(sv[e4 * 4 + 0]), a.scale_log2e, -l4.x));
+                        p[h2 * 32 + e4 * 4 + 1] = ex2_fast(fmaf(__uint_as_float(sv[e4 * 4 + 1]), a.scale_log2e, -l4.y));
+                        p[h2 * 32 + e4 * 4 + 2] = ex2_fast(fmaf(__uint_as_float(sv[e4 * 4 + 2]), a.scale_log2e, -l4.z));
+                        p[h2 * 32 + e4 * 4 + 3] = ex2_fast(fmaf(__uint_as_float(sv[e4 * 4 + 3]), a.scale_log2e, -l4.w));
+                    }
+                } else {
+                    const bool diag = (i == j);
+                    #pragma unroll
+                    for (int e4 = 0; e4 < 8; e4++) {
+                        const float4 l4 = *reinterpret_cast<const float4*>(stat + h2 * 32 + e4 * 4);
+                        const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
+                        #pragma unroll
+                        for (int k = 0; k < 4; k++) {
+                            const int e = h2 * 32 + e4 * 4 + k;
+                            float v = ex2_fast(fmaf(__uint_as_float(sv[e4 * 4 + k]), a.scale_log2e, -lv[k]));
+                            if (diag && hf * 64 + e < r) v = 0.f;
+                            p[e] = row_ok ? v : 0.f;
+                        }
+                    }
                 }
             }
-            uint32_t pk[32];
-            #pragma unroll
-            for (int e = 0; e < 32; e++) pk[e] = pack_bf16x2(p[2 * e], p[2 * e + 1]);
+            {
+                uint32_t pk[32];
+                #pragma unroll
+                for (int e = 0; e < 32; e++) pk[e] = pack_bf16x2(p[2 * e], p[2 * e + 1]);
+                tmem_st16(tP + lane_off + hf * 32, pk);
+                tmem_st16(tP + lane_off + hf * 32 + 16, pk + 16);
+            }
             if (threadIdx.x == 128) TRACE(1, 2);
-            if (t > 0) ok = mbar_wait(p_empty, (t - 1) & 1, abort_flag, a.status, 0x6a2) && ok;      // dV(t-1) has read P^T(t-1)
-            tc_fence_after();
-            tmem_st16(tP + lane_off + hf * 32, pk);
-            tmem_st16(tP + lane_off + hf * 32 + 16, pk + 16);
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
@@ -403,7 +425,7 @@ attn_bwd1_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
             const int tq = pr.i * BT + rr;
             float l = INFINITY, d = 0.f;
             if (tq < a.T) { l = a.lse[(size_t)pr.bh * a.T + tq] * log2e; d = a.delta[(size_t)pr.bh * a.T + tq] * a.scale; }
-            ok = mbar_wait(&st_empty[tt & 1], ((tt >> 1) & 1) ^ 1, abort_flag, a.status, 0x6b0) && ok;
+            ok = mbar_wait_relaxed(&st_empty[tt & 1], ((tt >> 1) & 1) ^ 1, abort_flag, a.status, 0x6b0) && ok;
             float* tab = sStat + (tt & 1) * (2 * BT);
             tab[rr] = l; tab[BT + rr] = d;
             __syncwarp();
@@ -415,31 +437,38 @@ attn_bwd1_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
             const bool last = wk.last_of_tile();
             wk.next();
             if (wk.valid()) put_stats(wk, t + 1);        // the next pair's table, one pair ahead
-            // ---- the pair's dQ contribution: 64 fp32 of query row rr.  Slot order [group of 4 columns][row][4 floats]: the 32
-            //      lanes of a warp (32 consecutive rows) write 512 contiguous bytes per instruction
+            // ---- the pair's dQ contribution: 64 fp32 of query row rr, slot order [group of 4 columns][row][4 floats],
             if (threadIdx.x == 384) TRACE(2, 0);
-            ok = mbar_wait(dq_full, t & 1, abort_flag, a.status, 0x6b1) && ok;
+            ok = mbar_wait_relaxed(dq_full, t & 1, abort_flag, a.status, 0x6b1) && ok;
             tc_fence_after();
             if (threadIdx.x == 384) TRACE(2, 1);
-            float* slot = a.dq_ws + ((size_t)bh * npairs + (size_t)(i * (i + 1) / 2 + j)) * SLOT_FLOATS + rr * 4;
-            const bool row_in = i * BT + rr < a.T;
+            // through the staging buffer and one bulk copy: 16 global stores per thread and pair through the load/store unit held up
+            // the shared-memory reads of the softmax warps for about a thousand cycles per pair (measured)
+            float* slot = a.dq_ws + ((size_t)bh * npairs + (size_t)(i * (i + 1) / 2 + j)) * SLOT_FLOATS;
+            if (staged) { if (issuer) tma_store_wait_read<0>(); asm volatile("bar.sync 1, 128;" ::: "memory"); }      // the previous copy has read the buffer
             #pragma unroll
             for (int c = 0; c < 2; c++) {
                 uint32_t v[32];
                 tmem_ld32(tdQ + lane_off + c * 32, v);
                 tmem_ld_wait();
                 if (c == 1) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(dq_empty); }
-                if (row_in && ok) {
-                    #pragma unroll
-                    for (int e = 0; e < 8; e++)
-                        __stcg(reinterpret_cast<uint4*>(slot + (c * 8 + e) * (BT * 4)), make_uint4(v[4 * e], v[4 * e + 1], v[4 * e + 2], v[4 * e + 3]));
-                }
+                #pragma unroll
+                for (int e = 0; e < 8; e++)
+                    *reinterpret_cast<uint4*>(sOut + (c * 8 + e) * (BT * 16) + rr * 16) = make_uint4(v[4 * e], v[4 * e + 1], v[4 * e + 2], v[4 * e + 3]);
             }
+            fence_async_smem();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (issuer && ok) {
+                asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                             ::"l"(slot), "r"(smem_u32(sOut)), "r"(SLOT_FLOATS * 4) : "memory");
+                tma_store_commit();
+            }
+            staged = true;
             if (threadIdx.x == 384) TRACE(2, 2);
             if (last) {
                 // ---- end of a key tile: dV_j and dK_j as bf16 tiles in the layout of a 128-byte-swizzled TMA box, one bulk store
                 //      each (rows past T are clipped by TMA); a warp writing rows itself would touch 32 cache lines per instruction
-                ok = mbar_wait(acc_full, kvt & 1, abort_flag, a.status, 0x6b2) && ok;
+                ok = mbar_wait_relaxed(acc_full, kvt & 1, abort_flag, a.status, 0x6b2) && ok;
                 tc_fence_after();
                 if (staged) { if (issuer) tma_store_wait_read<0>(); asm volatile("bar.sync 1, 128;" ::: "memory"); }
                 #pragma unroll

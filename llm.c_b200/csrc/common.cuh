@@ -217,6 +217,35 @@ DEVINL bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, 
     }
 }
 
+// try_wait with a suspend-time hint: the hardware parks the thread until the phase completes or about `ns` nanoseconds have
+// passed, instead of the thread polling.
+DEVINL bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(ns) : "memory");
+    return ok != 0;
+}
+// The same bounded wait for roles that wait long: each poll parks the thread in hardware (up to ~20 us), so the waiting warp takes
+// no issue slots and makes no shared-memory traffic while it waits.
+DEVINL bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, volatile int* abort_flag, unsigned int* status, unsigned int where,
+                              unsigned int unused = 0) {
+    (void)unused;
+    if (mbar_try_wait(bar, parity)) return true;
+    long long t0 = clock64();
+    while (true) {
+        if (mbar_try_wait_hint(bar, parity, 20000u)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+            *abort_flag = 1;
+            record_error(status, ST_MBAR_TIMEOUT, where);
+            return false;
+        }
+    }
+}
+
 // ----------------------------------------------------------------------------
 // TMA (bulk tensor copies, never with cluster multicast)
 
