@@ -184,6 +184,14 @@ def config_record(a, world, zero_stage):
             "l2": "no flush: every kernel's working set (activations 20+ GB per micro-step) exceeds the 126 MB L2"}
 
 
+def mfu_measured(model_flops_per_gpu):
+    """Model FLOP/s per GPU as a fraction of the sustained bf16 matmul peak measured on this machine class (MEASURED_PEAKS.json at
+    the repository root, written by the benchmark driver); None if that file is absent."""
+    from llmc_b200.utils import mfu
+    peak = mfu.measured_peak_tflops()
+    return model_flops_per_gpu / (peak * 1e12) if peak > 0 else None
+
+
 def env_rank():
     return int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
 
@@ -285,6 +293,7 @@ def run_ours(a):
                     "h2d_bytes_per_step": G * 2 * a.batch * a.seq * 4, "d2h_bytes_per_step": 8, "loss": last["loss"] if last else None},
             "gpu_launches": launches,
             "mfu_vs_2250_tflops": value / world * flops_tok / 2.25e15,
+            "mfu_vs_measured_sustained_peak": mfu_measured(value / world * flops_tok),
             "kernel_status": status,
             "impl": "ours",
         }

@@ -132,19 +132,30 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FwdArgs a) {
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
+        // The whole warp runs the issuing code in uniform control flow and one elected lane executes the tcgen05 instructions: a
+        // single lane inside a divergent branch has to move every descriptor from its registers to uniform registers, which costs
+        // it about 90 cycles per product (measured), more than a 128 x 64 x 16 product runs.  Wait results go through a warp vote
+        // so that the compiler knows the branches on them to be uniform; descriptors are built once and advanced by addition.
+        {
+            const bool leader = elect_one();
+#define WAIT_ALL(bar, parity, code) (__all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, a.status, code)) != 0)
             constexpr uint32_t idesc_s = umma_idesc_bf16(BQ, BKV, 0, 0);     // Q (K-major) x K (K-major)
             constexpr uint32_t idesc_o = umma_idesc_bf16(BQ, HSP, 0, 1);     // P (K-major) x V (N-major)
+            constexpr uint32_t TILE_UNITS = TILE_BYTES / 16, P_UNITS = P_BYTES / 16;
+            const uint64_t dQ0 = umma_desc_sw128(smem_u32(sQ), 16, 1024), dK0 = umma_desc_sw128(smem_u32(sK), 16, 1024);
+            const uint64_t dP0 = umma_desc_sw128(smem_u32(sP), 16, 1024), dV0 = umma_desc_sw128(smem_u32(sV), CHUNK_BYTES, 1024);
             auto issue_s = [&](int st, int qb, bool last_of_item) {
-                const uint32_t q = smem_u32(sQ + qb * TILE_BYTES), k = smem_u32(sK + st * TILE_BYTES);
-                #pragma unroll
-                for (int kk = 0; kk < HSP / 16; kk++) {      // 64-channel chunks are 16 KB apart, 16 channels = 32 bytes inside a chunk
-                    const uint32_t off = (kk >> 2) * CHUNK_BYTES + (kk & 3) * 32;
-                    umma_ss(tS, umma_desc_sw128(q + off, 16, 1024), umma_desc_sw128(k + off, 16, 1024), idesc_s, kk > 0);
+                const uint64_t q = dQ0 + (uint32_t)qb * TILE_UNITS, k = dK0 + (uint32_t)st * TILE_UNITS;
+                if (leader) {
+                    #pragma unroll
+                    for (int kk = 0; kk < HSP / 16; kk++) {      // 64-channel chunks are 16 KB apart, 16 channels = 32 bytes inside a chunk
+                        const uint32_t off = ((kk >> 2) * CHUNK_BYTES + (kk & 3) * 32) / 16;
+                        umma_ss(tS, q + off, k + off, idesc_s, kk > 0);
+                    }
+                    umma_commit(s_full);
+                    umma_commit(&k_empty[st]);
+                    if (last_of_item) umma_commit(&q_empty[qb]);
                 }
-                umma_commit(s_full);
-                umma_commit(&k_empty[st]);
-                if (last_of_item) umma_commit(&q_empty[qb]);
             };
             uint32_t t = 0;
             int cst = 0; uint32_t cph = 0;        // K/V ring position of tile t
@@ -152,7 +163,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FwdArgs a) {
             bool ok = true;
             if ((int)blockIdx.x < total) {
                 int qi, b, h; decode(blockIdx.x, qi, b, h);
-                ok = mbar_wait(&q_full[0], 0, abort_flag, a.status, 0x510) && mbar_wait(&k_full[0], 0, abort_flag, a.status, 0x511);
+                ok = WAIT_ALL(&q_full[0], 0, 0x510) && WAIT_ALL(&k_full[0], 0, 0x511);
                 tc_fence_after();
                 if (ok) issue_s(0, 0, qi == 0);
             }
@@ -167,31 +178,33 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQKV, const FwdArgs a) {
                     }
                     if (have_next) {
                         const int nit = it + (new_item ? 1 : 0);
-                        if (new_item) ok = ok && mbar_wait(&q_full[nit % QBUF], (nit / QBUF) & 1, abort_flag, a.status, 0x516);
+                        if (new_item) ok = ok && WAIT_ALL(&q_full[nit % QBUF], (nit / QBUF) & 1, 0x516);
                         int nst = cst + 1; uint32_t nph = cph;
                         if (nst == KVSTAGES) { nst = 0; nph ^= 1; }
-                        ok = ok && mbar_wait(&k_full[nst], nph, abort_flag, a.status, 0x512);
-                        ok = ok && mbar_wait(s_empty, t & 1, abort_flag, a.status, 0x513);
+                        ok = ok && WAIT_ALL(&k_full[nst], nph, 0x512);
+                        ok = ok && WAIT_ALL(s_empty, t & 1, 0x513);
                         if (!ok) break;
                         tc_fence_after();
                         issue_s(nst, nit % QBUF, nj == nqi);
                     }
-                    ok = ok && mbar_wait(p_full, t & 1, abort_flag, a.status, 0x514);
-                    ok = ok && mbar_wait(&v_full[cst], cph, abort_flag, a.status, 0x515);
+                    ok = ok && WAIT_ALL(p_full, t & 1, 0x514);
+                    ok = ok && WAIT_ALL(&v_full[cst], cph, 0x515);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t p = smem_u32(sP + (t % PBUF) * P_BYTES), v = smem_u32(sV + cst * TILE_BYTES);
-                    #pragma unroll
-                    for (int kk = 0; kk < BKV / 16; kk++) {
-                        // P: two 64-column swizzled chunks of 16 KB; V: 128 kv rows of 128 B, 16 rows per K step
-                        const uint32_t pa = p + (kk >> 2) * (BQ * 128) + (kk & 3) * 32;
-                        umma_ss(tO + (t & 1) * HSP, umma_desc_sw128(pa, 16, 1024), umma_desc_sw128(v + kk * 2048, CHUNK_BYTES, 1024), idesc_o, kk > 0);
+                    const uint64_t p = dP0 + (uint32_t)(t % PBUF) * P_UNITS, v = dV0 + (uint32_t)cst * TILE_UNITS;
+                    if (leader) {
+                        #pragma unroll
+                        for (int kk = 0; kk < BKV / 16; kk++) {
+                            // P: two 64-column swizzled chunks of 16 KB; V: 128 kv rows of 128 B, 16 rows per K step
+                            umma_ss(tO + (t & 1) * HSP, p + ((kk >> 2) * (BQ * 128) + (kk & 3) * 32) / 16, v + kk * 128, idesc_o, kk > 0);
+                        }
+                        umma_commit(&o_full[t & 1]);
+                        umma_commit(&v_empty[cst]);
                     }
-                    umma_commit(&o_full[t & 1]);
-                    umma_commit(&v_empty[cst]);
                     if (++cst == KVSTAGES) { cst = 0; cph ^= 1; }
                 }
             }
+#undef WAIT_ALL
         }
     } else {
         // softmax: thread = query row r x 32-column quarter cq of the S tile; it also owns 16 of the 64 output columns.

@@ -248,6 +248,7 @@ class Trainer:
         self._sample_model = None
         self._sample_gen = None
         self._have_batch = False
+        self._measured_peak = None
         from .utils.watchdog import StepWatchdog
         self.watchdog = StepWatchdog(c.output_log_dir, d.process_rank, d.num_processes, c.watchdog_s).start()
         m.allocate_activations(B, T)
@@ -499,6 +500,8 @@ class Trainer:
                 tps = tokens / dt
                 self.ema_tokens_per_second = tps if self.ema_tokens_per_second == 0.0 else 0.95 * self.ema_tokens_per_second + 0.05 * tps
             mfu_v = mfu.estimate_mfu(self.model.flops_per_token(c.T), tokens // d.num_processes, dt, self.device_name, self.precision)
+            # the MFU column is against the data-sheet peak of the device (2250 dense bf16 TFLOP/s on a B200), as the reference
+            # prints it; the JSONL metrics also carry the fraction of the measured sustained matmul peak of this machine class
             p("step %4d/%d | loss %7.6f (%+.2fz)| norm %6.4f (%+.2fz)| lr %.2e | %.2f ms | %.1f%% %s MFU | %.0f tok/s" % (
                 step + 1, self.train_num_batches, r["loss"], r["zloss"], r["grad_norm"], r["zgrad"], r["lr"], dt * 1000.0, 100.0 * mfu_v,
                 self.precision, self.ema_tokens_per_second))
@@ -507,7 +510,12 @@ class Trainer:
                     self.telemetry = mfu.GPUTelemetry(d.local_device_idx)
                 p(mfu.GPUTelemetry.format(self.telemetry.read()))
             self.logger.log_train(step, r["loss"], r["lr"], r["grad_norm"])
-            self.logger.log_metrics(step=step, loss=r["loss"], grad_norm=r["grad_norm"], lr=r["lr"], ms=dt * 1000.0, mfu=mfu_v)
+            if self._measured_peak is None:
+                self._measured_peak = mfu.measured_peak_tflops()
+            mfu_measured = (self.model.flops_per_token(c.T) * (tokens // d.num_processes) / dt / (self._measured_peak * 1e12)
+                            if self._measured_peak > 0 and self.precision == "bf16" else -1.0)
+            self.logger.log_metrics(step=step, loss=r["loss"], grad_norm=r["grad_norm"], lr=r["lr"], ms=dt * 1000.0, mfu=mfu_v,
+                                    mfu_of_measured_peak=mfu_measured)
         p("total average iteration speed: %.0f tok/s (EMA)" % self.ema_tokens_per_second)
 
     def close(self):

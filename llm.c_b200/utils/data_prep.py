@@ -76,3 +76,89 @@ def render_mmlu(rows, encode):
 
 def write_eval(path, examples):
     write_evalfile(path, examples)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# per-dataset entry points (reference: dev/data/{tinyshakespeare,tinystories,fineweb,hellaswag,mmlu}.py).  The reference's
+# scripts download their input; here the input is a local file that the user has fetched, so the scripts run offline.
+
+def get_encoder(name):
+    """'gpt2' -> tiktoken's GPT-2 encoding (must be installed with its vocabulary cached); 'bytes' -> one token per UTF-8 byte
+    (for smoke tests: ids 0..255, end of text 256)."""
+    if name == "bytes":
+        return (lambda s: list(s.encode("utf-8"))), 256
+    if name == "gpt2":
+        try:
+            import tiktoken
+        except ImportError as e:
+            raise SystemExit("the gpt2 encoder needs the tiktoken package (and its cached vocabulary): %s" % e)
+        enc = tiktoken.get_encoding("gpt2")
+        return (lambda s: enc.encode_ordinary(s)), enc._special_tokens["<|endoftext|>"]
+    raise SystemExit("unknown encoder %r (gpt2 | bytes)" % name)
+
+
+def prepare_tinyshakespeare(text_path, out_prefix, encode, eot, val_tokens=32768):
+    """One text file; blank-line separated sections each start with the end-of-text token; the first ``val_tokens`` tokens are
+    the validation split (reference: dev/data/tinyshakespeare.py:40-66)."""
+    with open(text_path) as f:
+        text = f.read()
+    toks = []
+    for section in text.split("\n\n"):
+        toks.append(eot)
+        toks.extend(encode(section + "\n\n"))
+    return write_split(toks, out_prefix, val_tokens)
+
+
+def prepare_tinystories(json_paths, out_prefix, encode, eot, shard_size=10 ** 8):
+    """TinyStories json shards (lists of {"story": ...}); first shard of the output is the validation split."""
+    def docs():
+        for p in json_paths:
+            with open(p) as f:
+                for ex in json.load(f):
+                    yield ex["story"].strip()
+    return shard_documents(docs(), encode, out_prefix, eot, shard_size)
+
+
+def prepare_fineweb(jsonl_paths, out_prefix, encode, eot, shard_size=10 ** 8):
+    """FineWeb / FineWeb-EDU as jsonl with a "text" field per line -> 100 M-token shards, shard 0 = validation
+    (reference: dev/data/fineweb.py:96-143)."""
+    def docs():
+        for p in jsonl_paths:
+            with open(p) as f:
+                for line in f:
+                    if line.strip():
+                        yield json.loads(line)["text"]
+    return shard_documents(docs(), encode, out_prefix, eot, shard_size)
+
+
+def main(argv=None):
+    import argparse
+    ap = argparse.ArgumentParser(description="tokenize a local copy of one of the reference's datasets into .bin files")
+    ap.add_argument("dataset", choices=["tinyshakespeare", "tinystories", "fineweb", "hellaswag", "mmlu"])
+    ap.add_argument("inputs", nargs="+", help="local input file(s): text, json shards, jsonl, HellaSwag jsonl, MMLU json rows")
+    ap.add_argument("-o", "--out", required=True, help="output prefix (train/val shards) or output file (eval sets)")
+    ap.add_argument("--encoder", default="gpt2")
+    ap.add_argument("--shard-size", type=int, default=10 ** 8)
+    a = ap.parse_args(argv)
+    encode, eot = get_encoder(a.encoder)
+    if a.dataset == "tinyshakespeare":
+        files = prepare_tinyshakespeare(a.inputs[0], a.out, encode, eot)
+    elif a.dataset == "tinystories":
+        files = prepare_tinystories(a.inputs, a.out, encode, eot, a.shard_size)
+    elif a.dataset == "fineweb":
+        files = prepare_fineweb(a.inputs, a.out, encode, eot, a.shard_size)
+    elif a.dataset == "hellaswag":
+        write_eval(a.out, render_hellaswag(a.inputs[0], encode))
+        files = [a.out]
+    else:
+        with open(a.inputs[0]) as f:
+            write_eval(a.out, render_mmlu(json.load(f), encode))
+        files = [a.out]
+    for p in files:
+        print("wrote %s" % p)
+    return 0
+
+
+if __name__ == "__main__":
+    import sys
+    sys.exit(main())

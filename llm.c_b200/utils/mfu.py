@@ -25,6 +25,21 @@ def get_flops_promised(device_name, precision="bf16"):
     return -1.0
 
 
+def measured_peak_tflops(path=None):
+    """Sustained bf16 matmul TFLOP/s measured on this machine class, from ``MEASURED_PEAKS.json`` at the repository root (written by
+    the benchmark driver: a seconds-long cuBLAS loop under the power cap), or -1 if the file is absent."""
+    import json
+    import os
+    if path is None:
+        path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        return float(d.get("bf16_tflops_sustained") or d.get("bf16_tflops") or -1.0)
+    except (OSError, ValueError):
+        return -1.0
+
+
 def estimate_mfu(flops_per_token, tokens, dt_seconds, device_name, precision="bf16"):
     """(6 N + 6 L C T) * tokens / dt / peak, or -1 if the peak is unknown (reference train_gpt2.cu:1126-1153)."""
     peak = get_flops_promised(device_name, precision)

@@ -17,7 +17,7 @@ from llmc_b200.train import TrainConfig, Trainer  # noqa: E402
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--dir", required=True)
-    ap.add_argument("--log", required=True)
+    ap.add_argument("--run-name", dest="log", required=True)
     ap.add_argument("--steps", type=int, required=True)        # train until this step number
     ap.add_argument("--checkpoint-at", type=int, default=0)
     ap.add_argument("--resume", type=int, default=0)

@@ -46,7 +46,7 @@ def test_resume_is_bit_identical(tmp_path, world, backend):
         pytest.skip("needs %d GPUs" % world)
     files(tmp_path)
     full, resumed = str(tmp_path / "full.json"), str(tmp_path / "resumed.json")
-    common = ["--dir", str(tmp_path), "--log", "run", "--backend", backend]
+    common = ["--dir", str(tmp_path), "--run-name", "run", "--backend", backend]
     run(world, common + ["--steps", "20", "--checkpoint-at", "10", "--out", full], 29581)
     assert os.path.exists(tmp_path / "run" / "DONE_00000010")
     for r in range(world):
