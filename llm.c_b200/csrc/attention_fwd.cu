@@ -348,7 +348,8 @@ int launch_fwd(const CUtensorMap& tm, const FwdArgs& a, int grid, cudaStream_t s
 }
 
 // out (B,T,NH,HS) = causal softmax(Q K^T / sqrt(HS)) V ; lse (B,NH,T) fp32.  Head sizes: multiples of 8 up to 128.
-extern "C" int llmc_attention_fwd(bf16* out, float* lse, const bf16* qkv, int B, int T, int NH, int hs, cudaStream_t stream) {
+// The entry point llmc_attention_fwd (attention_fwd1.cu) sends every head size but 64 here.
+int llmc_attention_fwd_general(bf16* out, float* lse, const bf16* qkv, int B, int T, int NH, int hs, cudaStream_t stream) {
     if (hs < 64 || hs > 128 || (hs % 8)) { fprintf(stderr, "[llmc_b200] attention: head size %d not supported (multiples of 8 from 64 to 128)\n", hs); return -1; }
     CUtensorMap tm;
     int rc = llmc_attn_qkv_map(&tm, qkv, B, T, NH, hs);
