@@ -62,10 +62,12 @@ def main():
 
     def step_p2p():
         seq[0] += 1
-        _lib.check(lib.llmc_p2p_reduce_scatter(c_g, c_s, offs, sizes, slices, r, N, 0, seq[0], ctypes.c_void_p(partials.data_ptr()), ctas, 1, stream), "rs")
-        torch.sum(partials, dim=0, keepdim=True, out=norm_sq)
+        _lib.check(lib.llmc_p2p_reduce_scatter(c_g, c_s, offs, sizes, slices, r, N, 0, seq[0], ctypes.c_void_p(partials.data_ptr()), ctas, 1, 0, None,
+                                               stream), "rs")
         seq[1] += 1
-        _lib.check(lib.llmc_p2p_allreduce_scalar(c_s, ctypes.c_void_p(norm_sq.data_ptr()), r, N, seq[1], stream), "ar")
+        # one launch: sum of the partial sums of squares, then the exchange over the ranks
+        _lib.check(lib.llmc_p2p_allreduce_scalars(c_s, ctypes.c_void_p(norm_sq.data_ptr()), 1, ctypes.c_void_p(partials.data_ptr()), partials.numel(),
+                                                  None, 0, 1.0, r, N, seq[1], stream), "ar")
         _lib.check(lib.llmc_p2p_adamw_allgather(c_p, c_s, kernels._p(master), kernels._p(grads), kernels._p(m), kernels._p(v), ctypes.byref(tab), r, N,
                                                 6e-4, 0.9, 0.95, 1e-8, 1, 1.0, kernels._p(norm_sq), 1.0, seq[0], kernels._p(counter), ctas, 0, stream), "adamw_ag")
         _lib.check(lib.llmc_p2p_wait(c_s, r, N, 0, 0, seq[0], stream), "wait")

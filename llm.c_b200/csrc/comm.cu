@@ -95,15 +95,20 @@ DEVINL bool wait_flag_ge(const unsigned long long* p, unsigned long long want, u
 // GPUs with one micro-step per step it was 1.3 % slower end to end (74.4 against 73.4 ms), so it is only kept selectable.
 constexpr int RS_THREADS = 128;
 
-template <int THREADS>
+// U packs of 8 elements per thread and trip, from up to NMAX ranks each: U * NMAX = 8 independent 16-byte loads are in flight per
+// thread whatever the number of ranks (NVLink latency is what this loop hides; with two ranks and one pack per trip the link
+// ran at a quarter of its rate).
+template <int THREADS, int U, int NMAX>
 __global__ void __launch_bounds__(THREADS, THREADS == RS_THREADS ? 10 : 1)
 reduce_scatter_kernel(PeerPtrs grads, PeerPtrs sig, SliceList sl, int rank, int N, float scale, int channel,
                       unsigned long long seq, float* __restrict__ norm_partials, int wait_peers, int allreduce,
                       unsigned int* __restrict__ done_counter, unsigned int* status) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     unsigned long long* my_sig = reinterpret_cast<unsigned long long*>(sig.p[rank]);
+    // wait_peers == 2: the exchange of "gradients final" flags already happened in rs_handshake_kernel, launched before this
+    // kernel, so that no SM is held while the slowest peer is still computing.
     // 1. tell every peer that this rank's gradients of `channel` are final (one warp of block 0)
-    if (blockIdx.x == 0 && threadIdx.x < N) {
+    if (wait_peers != 2 && blockIdx.x == 0 && threadIdx.x < N) {
         __threadfence_system();
         unsigned long long* peer = reinterpret_cast<unsigned long long*>(sig.p[threadIdx.x]);
         st_release_sys(peer + SIG_RS_BASE + channel * MAX_RANKS + rank, seq);
@@ -111,7 +116,7 @@ reduce_scatter_kernel(PeerPtrs grads, PeerPtrs sig, SliceList sl, int rank, int 
     // 2. the first warp waits for every peer's signal (lane p polls peer p; few pollers: every poll is a system-scope load that
     //    goes to L2); the verdict reaches the other warps through the barrier itself, so no shared memory is needed
     bool ok = true;
-    if (wait_peers) {
+    if (wait_peers == 1) {
         bool mine_ok = true;
         if (warp == 0 && lane < N) mine_ok = wait_flag_ge(my_sig + SIG_RS_BASE + channel * MAX_RANKS + lane, seq, status, 0x700 + lane);
         ok = __syncthreads_and(mine_ok) != 0;
@@ -123,40 +128,54 @@ reduce_scatter_kernel(PeerPtrs grads, PeerPtrs sig, SliceList sl, int rank, int 
             const long long shard = sl.size[s] / N;
             const long long base = sl.off[s] + (long long)rank * shard;
             const long long packs = shard >> 3;
-            for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < packs; i += (long long)gridDim.x * blockDim.x) {
-                float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                // rank order: the same sum on every run.  The whole-SM CTAs keep all peers' loads in flight at once (NVLink latency
-                // is what this loop hides); the small CTAs have the registers for four at a time.
-                constexpr int GROUP = THREADS == RS_THREADS ? 4 : MAX_RANKS;
+            for (long long i0 = (long long)blockIdx.x * (THREADS * U) + threadIdx.x; i0 < packs; i0 += (long long)gridDim.x * (THREADS * U)) {
+                float sum[U][8];
                 #pragma unroll
-                for (int p0 = 0; p0 < MAX_RANKS; p0 += GROUP) {
+                for (int u = 0; u < U; u++)
+                    #pragma unroll
+                    for (int e = 0; e < 8; e++) sum[u][e] = 0.f;
+                // rank order: the same sum on every run.  The small CTAs have the registers for four vectors at a time.
+                constexpr int GROUP = THREADS == RS_THREADS ? 4 : NMAX;
+                #pragma unroll
+                for (int p0 = 0; p0 < NMAX; p0 += GROUP) {
                     if (p0 < N) {
-                        bf16x8 v[GROUP];
+                        bf16x8 v[U][GROUP];
                         #pragma unroll
-                        for (int k = 0; k < GROUP; k++)
-                            if (p0 + k < N) v[k] = ld128cs(reinterpret_cast<const bf16*>(grads.p[p0 + k]) + base + i * 8);
+                        for (int u = 0; u < U; u++)
+                            #pragma unroll
+                            for (int k = 0; k < GROUP; k++)
+                                if (p0 + k < N && i0 + u * THREADS < packs)
+                                    v[u][k] = ld128cs(reinterpret_cast<const bf16*>(grads.p[p0 + k]) + base + (i0 + u * THREADS) * 8);
                         #pragma unroll
-                        for (int k = 0; k < GROUP; k++) {
-                            if (p0 + k < N) {
-                                #pragma unroll
-                                for (int e = 0; e < 8; e++) sum[e] += __bfloat162float(v[k][e]);
+                        for (int u = 0; u < U; u++)
+                            #pragma unroll
+                            for (int k = 0; k < GROUP; k++) {
+                                if (p0 + k < N && i0 + u * THREADS < packs) {
+                                    #pragma unroll
+                                    for (int e = 0; e < 8; e++) sum[u][e] += __bfloat162float(v[u][k][e]);
+                                }
                             }
-                        }
                     }
                 }
-                bf16x8 o;
                 #pragma unroll
-                for (int e = 0; e < 8; e++) {
-                    o[e] = __float2bfloat16_rn(sum[e] * scale);
-                    const float f = __bfloat162float(o[e]);
-                    acc_sq += f * f;
-                }
-                if (allreduce) {
-                    #pragma unroll
-                    for (int p = 0; p < MAX_RANKS; p++)
-                        if (p < N) st128(reinterpret_cast<bf16*>(grads.p[p]) + base + i * 8, o);      // own copy and every peer's
-                } else {
-                    st128(mine + base + i * 8, o);
+                for (int u = 0; u < U; u++) {
+                    const long long i = i0 + u * THREADS;
+                    if (i < packs) {
+                        bf16x8 o;
+                        #pragma unroll
+                        for (int e = 0; e < 8; e++) {
+                            o[e] = __float2bfloat16_rn(sum[u][e] * scale);
+                            const float f = __bfloat162float(o[e]);
+                            acc_sq += f * f;
+                        }
+                        if (allreduce) {
+                            #pragma unroll
+                            for (int p = 0; p < NMAX; p++)
+                                if (p < N) st128(reinterpret_cast<bf16*>(grads.p[p]) + base + i * 8, o);      // own copy and every peer's
+                        } else {
+                            st128(mine + base + i * 8, o);
+                        }
+                    }
                 }
             }
         }
@@ -314,6 +333,19 @@ __global__ void wait_flags_kernel(PeerPtrs sig, int rank, int N, int base, int n
             if (!wait_flag_ge(my_sig + base + ch * MAX_RANKS + p, seq, status, 0x740 + p)) break;
 }
 
+// One warp: tells every peer that this rank's gradients of `channel` are final and waits until every peer has said the same.
+// It runs ahead of the wide reduction on the communication stream; while it waits it occupies one warp slot, not 32 SMs.
+__global__ void __launch_bounds__(32) rs_handshake_kernel(PeerPtrs sig, int rank, int N, int channel, unsigned long long seq, unsigned int* status) {
+    const int lane = threadIdx.x;
+    if (lane < N) {
+        __threadfence_system();
+        unsigned long long* peer = reinterpret_cast<unsigned long long*>(sig.p[lane]);
+        st_release_sys(peer + SIG_RS_BASE + channel * MAX_RANKS + rank, seq);
+        const unsigned long long* my_sig = reinterpret_cast<const unsigned long long*>(sig.p[rank]);
+        wait_flag_ge(my_sig + SIG_RS_BASE + channel * MAX_RANKS + lane, seq, status, 0x720 + lane);
+    }
+}
+
 __global__ void signal_flags_kernel(PeerPtrs sig, int rank, int N, int base, unsigned long long seq) {
     if (threadIdx.x < N) {
         __threadfence_system();
@@ -352,6 +384,8 @@ static int rs_threads() {
 
 // Reduce-scatter (mean) of up to 16 slices of the gradient buffers. grad_ptrs / sig_ptrs: N device pointers (one per rank).
 // Every slice size must be a multiple of 8*N. norm_partials: llmc_p2p_rs_partials(ctas) floats (may be null).
+// wait_peers: 1 = the reduction kernel itself exchanges the "gradients final" flags and waits; 2 = llmc_p2p_rs_handshake already
+// did, in an earlier launch (the wide kernel then never spins); 0 = signal only (single-process tests).
 extern "C" int llmc_p2p_reduce_scatter(const unsigned long long* grad_ptrs, const unsigned long long* sig_ptrs, const long long* offs,
                                        const long long* sizes, int count, int rank, int N, int channel, unsigned long long seq,
                                        float* norm_partials, int ctas, int wait_peers, int allreduce, unsigned int* done_counter,
@@ -361,8 +395,24 @@ extern "C" int llmc_p2p_reduce_scatter(const unsigned long long* grad_ptrs, cons
     if (allreduce && done_counter == nullptr) return -1;
     sl.count = count;
     for (int i = 0; i < count; i++) { sl.off[i] = offs[i]; sl.size[i] = sizes[i]; if (sizes[i] % (8 * N) || offs[i] % 8) return -2; }
-    if (rs_threads() == 512) reduce_scatter_kernel<512><<<ctas, 512, 0, stream>>>(g, s, sl, rank, N, 1.0f / N, channel, seq, norm_partials, wait_peers, allreduce, done_counter, llmc_status_ptr());
-    else reduce_scatter_kernel<RS_THREADS><<<ctas, RS_THREADS, 0, stream>>>(g, s, sl, rank, N, 1.0f / N, channel, seq, norm_partials, wait_peers, allreduce, done_counter, llmc_status_ptr());
+#define RS_LAUNCH(T, U, NM) reduce_scatter_kernel<T, U, NM><<<ctas, T, 0, stream>>>(g, s, sl, rank, N, 1.0f / N, channel, seq, norm_partials, \
+                                                                                    wait_peers, allreduce, done_counter, llmc_status_ptr())
+    if (rs_threads() != 512) RS_LAUNCH(RS_THREADS, 1, 8);
+    else if (N <= 2) RS_LAUNCH(512, 4, 2);
+    else if (N <= 4) RS_LAUNCH(512, 2, 4);
+    else RS_LAUNCH(512, 1, 8);
+#undef RS_LAUNCH
+    CUDA_CHECK(cudaGetLastError());
+    return 0;
+}
+
+// The exchange of "gradients of `channel` are final" flags as a launch of its own (one warp).  A reduce-scatter launched with
+// wait_peers = 2 after it, on this stream or on one that waits for it, finds every peer's gradients final.
+extern "C" int llmc_p2p_rs_handshake(const unsigned long long* sig_ptrs, int rank, int N, int channel, unsigned long long seq,
+                                     cudaStream_t stream) {
+    PeerPtrs s;
+    if (fill(&s, sig_ptrs, N) || channel < 0 || channel >= 200) return -1;
+    rs_handshake_kernel<<<1, 32, 0, stream>>>(s, rank, N, channel, seq, llmc_status_ptr());
     CUDA_CHECK(cudaGetLastError());
     return 0;
 }

@@ -51,6 +51,8 @@ def _cfg_lib():
         lib.llmc_p2p_ag_flag_offset.argtypes = [I]
         lib.llmc_p2p_barrier.restype = I
         lib.llmc_p2p_barrier.argtypes = [P, I, I, U, P]
+        lib.llmc_p2p_rs_handshake.restype = I
+        lib.llmc_p2p_rs_handshake.argtypes = [P, I, I, I, U, P]
         _configured = True
     return lib
 
@@ -131,13 +133,23 @@ class P2PBackend:
         self.sig_t, self.sig_ptrs, self._sh = arena.alloc(words, torch.int64)
         self.c_params, self.c_grads, self.c_sig = _ptr_array(self.param_ptrs), _ptr_array(self.grad_ptrs), _ptr_array(self.sig_ptrs)
         dev = dist_cfg.device
-        self.stream = torch.cuda.Stream(device=dev)
+        # LLMC_RS_PRIORITY=-1 makes the communication stream a high-priority stream (its CTAs are placed first when SMs free up)
+        self.stream = torch.cuda.Stream(device=dev, priority=int(os.environ.get("LLMC_RS_PRIORITY", "0")))
         self.ctas = 32                  # x 4 = CTAs of the fused update + gather, which runs alone after backward
         # reduce-scatter: 32 whole-SM CTAs next to the backward pass (LLMC_RS_THREADS=128: one small CTA per SM instead)
-        self.rs_ctas = 32
+        self.rs_ctas = int(os.environ.get("LLMC_RS_CTAS", "32"))
         if os.environ.get("LLMC_RS_THREADS") == "128":
             self.rs_ctas = torch.cuda.get_device_properties(dev).multi_processor_count
-        self.rs_partials = self.lib.llmc_p2p_rs_partials(self.rs_ctas)
+        # the last reduction of a step (embeddings, final norm) runs after backward, alone on the GPU: it gets a wider grid
+        self.rs_tail_ctas = max(self.rs_ctas, int(os.environ.get("LLMC_RS_TAIL_CTAS", "128")))
+        # 2: a one-warp kernel exchanges the "gradients final" flags ahead of the wide kernel, which then never holds SMs while
+        # the slowest peer is still computing; 1: the wide kernel does it itself (kept selectable for measurements)
+        self.rs_wait_mode = 2 if os.environ.get("LLMC_RS_HANDSHAKE", "1") != "0" else 1
+        self.rs_partials = self.lib.llmc_p2p_rs_partials(self.rs_tail_ctas)     # per-channel stride; unused entries stay zero
+        self.rs_mode = os.environ.get("LLMC_RS_MODE", "deferred")               # "deferred" | "instream" | "side"
+        if self.rs_mode not in ("deferred", "instream", "side"):
+            raise ValueError("LLMC_RS_MODE must be deferred, instream or side")
+        self._pending = None
         self.num_channels = model.cfg.num_layers + 1
         self.norm_partials = torch.zeros(self.num_channels * self.rs_partials, dtype=torch.float32, device=dev)
         self.done_counter = torch.zeros(2, dtype=torch.int32, device=dev)      # [0] update + gather, [1] all-reduce (other stream)
@@ -152,21 +164,55 @@ class P2PBackend:
         dist.barrier()          # every rank's buffers are zeroed and mapped before any kernel touches a peer
 
     # ---- ZeRO-1 backend interface (see zero.py)
-    def reduce_tensors(self, grads_flat, slices, channel=None):
+    def reduce_tensors(self, grads_flat, slices, channel=None, tail=False):
         if not self.reduced_this_step:
             self.seq += 1
             self.reduced_this_step = True
         ch = self._channel_of(slices)
+        self._channels_this_step = max(getattr(self, "_channels_this_step", 0), ch + 1)
+        cur = torch.cuda.current_stream()
+        mode = self.rs_mode
+        if mode == "side":
+            # the whole reduction runs on the communication stream, beside the rest of backward
+            self.stream.wait_stream(cur)
+            if self.rs_wait_mode == 2:
+                self._handshake(ch, self.stream)
+            self._launch_reduce(slices, ch, self.rs_tail_ctas if tail else self.rs_ctas, self.rs_wait_mode, self.stream)
+            return
+        # "deferred": only the flag exchange runs on the communication stream (one warp, no SM held); the wide reduction of a
+        # layer is launched on the compute stream one layer later, when the exchange has normally long finished, so that it
+        # runs alone on the whole GPU for a few tens of microseconds instead of beside a persistent GEMM
+        self.stream.wait_stream(cur)
+        self._handshake(ch, self.stream)
+        ev = torch.cuda.Event()
+        ev.record(self.stream)
+        self._flush_pending(cur)
+        self._pending = (slices, ch, ev)
+        if tail or mode == "instream":
+            self._flush_pending(cur)
+
+    def _handshake(self, ch, stream):
+        kernels._launches += 1
+        check(self.lib.llmc_p2p_rs_handshake(self.c_sig, self.r, self.N, ch, self.seq, ctypes.c_void_p(stream.cuda_stream)),
+              "llmc_p2p_rs_handshake")
+
+    def _flush_pending(self, cur):
+        if self._pending is None:
+            return
+        slices, ch, ev = self._pending
+        self._pending = None
+        cur.wait_event(ev)
+        self._launch_reduce(slices, ch, self.rs_tail_ctas, 2, cur)
+
+    def _launch_reduce(self, slices, ch, ctas, wait_mode, stream):
         offs = (ctypes.c_longlong * len(slices))(*[s[0] for s in slices])
         sizes = (ctypes.c_longlong * len(slices))(*[s[1] for s in slices])
-        self.stream.wait_stream(torch.cuda.current_stream())
         kernels._launches += 1
         part = self.norm_partials[ch * self.rs_partials:(ch + 1) * self.rs_partials]
-        self._channels_this_step = max(getattr(self, "_channels_this_step", 0), ch + 1)
         check(self.lib.llmc_p2p_reduce_scatter(self.c_grads, self.c_sig, offs, sizes, len(slices), self.r, self.N, ch, self.seq,
-                                               ctypes.c_void_p(part.data_ptr()), self.rs_ctas, 1, int(self.zero_stage == 0),
+                                               ctypes.c_void_p(part.data_ptr()), ctas, wait_mode, int(self.zero_stage == 0),
                                                ctypes.c_void_p(self.done_counter.data_ptr() + 4),
-                                               ctypes.c_void_p(self.stream.cuda_stream)), "llmc_p2p_reduce_scatter")
+                                               ctypes.c_void_p(stream.cuda_stream)), "llmc_p2p_reduce_scatter")
 
     def _channel_of(self, slices):
         key = slices[0][0]
@@ -179,6 +225,7 @@ class P2PBackend:
 
     def finish_reduce(self):
         cur = torch.cuda.current_stream()
+        self._flush_pending(cur)
         cur.wait_stream(self.stream)
         if self.zero_stage == 0 and self.reduced_this_step:
             # data parallel without sharding: every peer's shard of the mean must have landed in this rank's buffer

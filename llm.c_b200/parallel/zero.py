@@ -26,7 +26,7 @@ class SingleBackend:
     """One process: nothing to communicate."""
     name = "single"
 
-    def reduce_tensors(self, grads_flat, slices, stream_event=None):
+    def reduce_tensors(self, grads_flat, slices, stream_event=None, tail=False):
         pass
 
     def finish_reduce(self):
@@ -59,7 +59,7 @@ class NcclBackend:
         self.stream = torch.cuda.Stream(device=cfg.device) if self.cuda else None
         self.avg = dist.ReduceOp.AVG if self.cuda else dist.ReduceOp.SUM     # gloo has no AVG
 
-    def reduce_tensors(self, grads_flat, slices, stream_event=None):
+    def reduce_tensors(self, grads_flat, slices, stream_event=None, tail=False):
         """slices: list of (offset, size) of whole per-layer tensors.  ZeRO-1: reduce-scatter in place (the owner's shard
         receives the mean); otherwise all-reduce."""
         def run():
@@ -179,7 +179,7 @@ class ShardedAdamW:
     # ---- gradient reduction, overlapped with backward
     def on_layer_grads_ready(self, layer):
         if self.N > 1:
-            self.backend.reduce_tensors(self.model.grads_flat, self.layer_slices[layer])
+            self.backend.reduce_tensors(self.model.grads_flat, self.layer_slices[layer], tail=(layer == -1))
 
     def views(self, weight_decay=0.0, seeds=None):
         out = []
