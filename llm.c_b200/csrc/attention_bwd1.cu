@@ -519,39 +519,62 @@ attn_bwd1_kernel(const __grid_constant__ CUtensorMap tmQKV, const __grid_constan
 }
 
 // dQ[b, t, h, :] = bf16( sum over j = 0..i of slot(j, i)[r, :] ), i = t / 128, r = t % 128, added in the order of j.
-// One thread per (row, 8 columns): two 16-byte loads per slot (slot order: [group of 4 columns][row][4 floats]), one
-// 16-byte store; the 8 lanes of a row write its 128 bytes together.
+// One CTA per (batch, head, query tile), heaviest tiles first.  A slot is read as it was written (order [group of 4 columns][row]
+// [4 floats]): a warp reads 512 contiguous bytes per instruction, every thread has 16 loads of 16 bytes in flight (two slots);
+// the sums are transposed through shared memory so that the 8 lanes of a row store its 128 bytes together.
 __global__ void __launch_bounds__(256)
 dq_fold_kernel(bf16* __restrict__ dqkv, const float* __restrict__ ws, int B, int T, int NH, int nt) {
-    const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    const int c8 = (int)(gid & 7);
-    const long long row = gid >> 3;                      // (bh, t)
-    if (row >= (long long)B * NH * T) return;
-    const int t = (int)(row % T);
-    const long long bh = row / T;
-    const int i = t / BT, r = t - i * BT;
+    __shared__ __align__(16) bf16 tile[BT][HS + 8];
+    const int nbh = B * NH;
+    const int i = nt - 1 - (int)(blockIdx.x / nbh);
+    const int bh = (int)(blockIdx.x % nbh);
     const int npairs = nt * (nt + 1) / 2;
-    const float* src = ws + ((size_t)bh * npairs + (size_t)(i * (i + 1) / 2)) * SLOT_FLOATS + (c8 * 2) * (BT * 4) + r * 4;
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    int j = 0;
-    for (; j + 1 <= i; j += 2) {                         // two slots in flight; the additions keep the order of j
-        const f32x4 a0 = ld128cs(src + (size_t)j * SLOT_FLOATS), a1 = ld128cs(src + (size_t)j * SLOT_FLOATS + BT * 4);
-        const f32x4 b0 = ld128cs(src + (size_t)(j + 1) * SLOT_FLOATS), b1 = ld128cs(src + (size_t)(j + 1) * SLOT_FLOATS + BT * 4);
-        #pragma unroll
-        for (int e = 0; e < 4; e++) { acc[e] += a0[e]; acc[e + 4] += a1[e]; }
-        #pragma unroll
-        for (int e = 0; e < 4; e++) { acc[e] += b0[e]; acc[e + 4] += b1[e]; }
-    }
-    for (; j <= i; j++) {
-        const f32x4 a0 = ld128cs(src + (size_t)j * SLOT_FLOATS), a1 = ld128cs(src + (size_t)j * SLOT_FLOATS + BT * 4);
-        #pragma unroll
-        for (int e = 0; e < 4; e++) { acc[e] += a0[e]; acc[e + 4] += a1[e]; }
-    }
-    const int b = (int)(bh / NH), h = (int)(bh - (long long)b * NH);
-    bf16x8 o;
+    const int t = threadIdx.x;
+    const float* src = ws + ((size_t)bh * npairs + (size_t)(i * (i + 1) / 2)) * SLOT_FLOATS + t * 4;
+    f32x4 acc[8];
     #pragma unroll
-    for (int e = 0; e < 8; e++) o[e] = __float2bfloat16_rn(acc[e]);
-    st128(dqkv + (((size_t)b * T + t) * 3) * NH * HS + (size_t)h * HS + c8 * 8, o);
+    for (int k = 0; k < 8; k++)
+        #pragma unroll
+        for (int e = 0; e < 4; e++) acc[k][e] = 0.f;
+    for (int j = 0; j <= i; j += 2) {
+        const bool two = j + 1 <= i;
+        f32x4 a0[8], a1[8];
+        #pragma unroll
+        for (int k = 0; k < 8; k++) a0[k] = ld128cs(src + (size_t)j * SLOT_FLOATS + k * 1024);
+        if (two) {
+            #pragma unroll
+            for (int k = 0; k < 8; k++) a1[k] = ld128cs(src + (size_t)(j + 1) * SLOT_FLOATS + k * 1024);
+        }
+        #pragma unroll
+        for (int k = 0; k < 8; k++)
+            #pragma unroll
+            for (int e = 0; e < 4; e++) acc[k][e] += a0[k][e];
+        if (two) {
+            #pragma unroll
+            for (int k = 0; k < 8; k++)
+                #pragma unroll
+                for (int e = 0; e < 4; e++) acc[k][e] += a1[k][e];
+        }
+    }
+    // thread t holds row t % 128, column groups 2k + t / 128
+    const int row = t & (BT - 1), g0 = t >> 7;
+    #pragma unroll
+    for (int k = 0; k < 8; k++) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(acc[k][0], acc[k][1]), hi = __floats2bfloat162_rn(acc[k][2], acc[k][3]);
+        uint2 w;
+        w.x = *reinterpret_cast<uint32_t*>(&lo);
+        w.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(&tile[row][(2 * k + g0) * 4]) = w;
+    }
+    __syncthreads();
+    const int b = bh / NH, h = bh - b * NH;
+    #pragma unroll
+    for (int q = 0; q < 4; q++) {
+        const int c = q * 256 + t, r = c >> 3, c8 = c & 7;
+        const int tq = i * BT + r;
+        if (tq < T)
+            *reinterpret_cast<uint4*>(dqkv + (((size_t)b * T + tq) * 3) * NH * HS + (size_t)h * HS + c8 * 8) = *reinterpret_cast<const uint4*>(&tile[r][c8 * 8]);
+    }
 }
 
 }  // namespace
@@ -608,8 +631,7 @@ extern "C" int llmc_attention_bwd(bf16* dqkv, float* ws, const bf16* dout, const
     }
     attn_bwd1_kernel<<<grid, THREADS, SMEM, stream>>>(tmQKV, tmDO, tmDQKV, a);
     CUDA_CHECK(cudaGetLastError());
-    const long long threads = (long long)B * NH * T * 8;
-    dq_fold_kernel<<<(unsigned)CEIL_DIV(threads, 256), 256, 0, stream>>>(dqkv, dq_ws, B, T, NH, nt);
+    dq_fold_kernel<<<(unsigned)(B * NH * nt), 256, 0, stream>>>(dqkv, dq_ws, B, T, NH, nt);
     CUDA_CHECK(cudaGetLastError());
     return 0;
 }
