@@ -87,6 +87,26 @@ def cuda():
         "llmc_attention_fwd": (I, [P, P, P, I, I, I, I, S]),
         "llmc_attention_bwd": (I, [P, P, P, P, P, P, I, I, I, I, S]),
         "llmc_attention_bwd_workspace": (L, [I, I, I, I]),
+        # full-precision operator set (csrc/fp32_ops.cu)
+        "llmc_f32_gelu_fwd": (I, [P, P, L, S]),
+        "llmc_f32_gelu_bwd": (I, [P, P, L, S]),
+        "llmc_f32_residual_add": (I, [P, P, P, L, S]),
+        "llmc_f32_encoder_fwd": (I, [P, P, P, P, I, I, I, I, S]),
+        "llmc_f32_encoder_bwd": (I, [P, P, P, P, I, I, I, I, I, I, S]),
+        "llmc_f32_layernorm_fwd": (I, [P, P, P, P, P, P, P, P, I, I, S]),
+        "llmc_f32_layernorm_bwd_scratch": (L, [I, I]),
+        "llmc_f32_layernorm_bwd": (I, [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, S]),
+        "llmc_f32_bias_grad_scratch": (L, [I, I]),
+        "llmc_f32_bias_grad": (I, [P, P, P, I, I, I, S]),
+        "llmc_f32_classifier": (I, [P, P, P, F, I, I, I, I, I, S]),
+        "llmc_f32_permute_qkv": (I, [P, P, I, I, I, I, I, S]),
+        "llmc_f32_permute_heads": (I, [P, P, I, I, I, I, I, S]),
+        "llmc_f32_softmax_causal": (I, [P, P, P, F, L, I, S]),
+        "llmc_f32_softmax_causal_bwd": (I, [P, P, F, L, I, S]),
+        "llmc_f32_adamw": (I, [P, P, P, P, P, L, L, L, L, L, I, F, F, F, I, F, F, F, P, F, S]),
+        "llmc_f32_sumsq_partials_per_slice": (I, []),
+        "llmc_f32_sumsq": (I, [P, P, L, L, L, I, S]),
+        "llmc_f32_copy_slices": (I, [P, P, L, L, L, L, L, I, S]),
     }
     for name, (res, args) in sigs.items():
         if hasattr(lib, name):

@@ -6,13 +6,16 @@ buffers) and exists in two implementations with the same signature:
 * ``kernels``    the hand-written sm_100a CUDA kernels (device tensors),
 * ``reference``  a plain PyTorch fp32 restatement (CPU tensors; also the numerics oracle of the tests).
 
+* ``kernels_fp32``  the full-precision kernels of the GPT-2 operator set (fp32 device tensors, the legacy ``-dt fp32`` mode).
+
 The functions exported here dispatch on the device and type of their first tensor argument: bf16 device tensors go
-to the sm_100a kernels and never fall back to PyTorch (if the kernel library is missing the call raises); fp32
-tensors, on the host or on a device (the legacy full-precision mode), go to the restatement.
+to the sm_100a kernels and never fall back to PyTorch (if the kernel library is missing the call raises); fp32 device
+tensors go to ``kernels_fp32`` (operators of the LLaMA family, which that module does not have, and the matmuls' IEEE fp32
+form run on PyTorch's library kernels on the device); host tensors go to the restatement.
 """
 import torch
 
-from . import kernels, reference
+from . import kernels, kernels_fp32, reference
 
 _NAMES = [
     "encoder_forward", "encoder_backward", "layernorm_forward", "fused_residual_forward", "layernorm_backward",
@@ -36,9 +39,16 @@ def _dispatch(name):
 
     by_device = name in _DECIDED_BY_DEVICE
 
+    f32 = getattr(kernels_fp32, name, None)
+
     def op(*args, **kwargs):
         t = args[which]
-        return (k if (t.is_cuda and (by_device or t.dtype != torch.float32)) else r)(*args, **kwargs)
+        if t.is_cuda:
+            if by_device or t.dtype != torch.float32:
+                return k(*args, **kwargs)
+            if f32 is not None:
+                return f32(*args, **kwargs)
+        return r(*args, **kwargs)
 
     op.__name__ = name
     op.__doc__ = k.__doc__
