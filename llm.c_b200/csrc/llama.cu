@@ -145,14 +145,35 @@ rms_bwd_kernel(bf16* __restrict__ dinp, float* __restrict__ partials, const bf16
     }
 }
 
-// dweight[c] (+)= sum over CTAs, in CTA order
-__global__ void rms_bwd_fold_kernel(bf16* __restrict__ dweight, const float* __restrict__ partials, int num_ctas, int C, int accumulate) {
-    const int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= C) return;
-    float a = 0.f;
-    for (int i = 0; i < num_ctas; i++) a += partials[(size_t)i * C + c];
-    if (accumulate) a += __bfloat162float(dweight[c]);
-    dweight[c] = __float2bfloat16_rn(a);
+// dweight[c] (+)= sum over CTAs of the partial sums: a block covers 16 channels (4 threads x 4 floats) with 64 slices of CTAs;
+// slice y adds CTAs y, y + 64, ... in order and the slices are added in order (a fixed tree, many loads in flight)
+constexpr int RMS_FOLD_SLICES = 64;
+__global__ void __launch_bounds__(4 * RMS_FOLD_SLICES)
+rms_bwd_fold_kernel(bf16* __restrict__ dweight, const float* __restrict__ partials, int num_ctas, int C, int accumulate) {
+    __shared__ float4 sh[RMS_FOLD_SLICES][4];
+    const int x = threadIdx.x & 3, y = threadIdx.x >> 2;
+    const int c = blockIdx.x * 16 + x * 4;
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (c < C) {
+        #pragma unroll 4
+        for (int i = y; i < num_ctas; i += RMS_FOLD_SLICES) {
+            const float4 v = __ldcs(reinterpret_cast<const float4*>(partials + (size_t)i * C + c));
+            a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+        }
+    }
+    sh[y][x] = a;
+    __syncthreads();
+    if (y == 0 && c < C) {
+        a = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int k = 0; k < RMS_FOLD_SLICES; k++) { const float4 v = sh[k][x]; a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w; }
+        const float av[4] = {a.x, a.y, a.z, a.w};
+        #pragma unroll
+        for (int e = 0; e < 4; e++) {
+            float va = av[e];
+            if (accumulate) va += __bfloat162float(dweight[c + e]);
+            dweight[c + e] = __float2bfloat16_rn(va);
+        }
+    }
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -342,7 +363,7 @@ extern "C" int llmc_rmsnorm_bwd(bf16* dinp, bf16* dweight, float* scratch, const
 #undef RMSB_PICK
 #undef RMSB_LAUNCH
     CUDA_CHECK(cudaGetLastError());
-    rms_bwd_fold_kernel<<<CEIL_DIV(C, 128), 128, 0, stream>>>(dweight, scratch, ctas, C, accumulate_dw);
+    rms_bwd_fold_kernel<<<CEIL_DIV(C, 16), 4 * RMS_FOLD_SLICES, 0, stream>>>(dweight, scratch, ctas, C, accumulate_dw);
     CUDA_CHECK(cudaGetLastError());
     return 0;
 }
