@@ -38,13 +38,18 @@ def cuda():
     global _cuda
     if _cuda is not None:
         return _cuda
-    lib = _load("libllmc_b200.so", "build_cuda")
+    if os.environ.get("LLMC_DEBUG_CHECKS") == "1":
+        # the kernels with their debug checks on (alignment of every 16-byte access, id ranges): see build.build_cuda_debug
+        lib = _load("libllmc_b200_debug.so", "build_cuda_debug")
+    else:
+        lib = _load("libllmc_b200.so", "build_cuda")
     P, I, L, F, U, S = c_void_p, c_int, c_longlong, c_float, c_uint, c_void_p
     U64 = ctypes.c_ulonglong
     sigs = {
         "llmc_status_read": (I, [I, POINTER(c_uint)]),
         "llmc_tensormap_cache_clear": (None, []),
         "llmc_device_sm_count": (I, []),
+        "llmc_debug_checks_enabled": (I, []),
         "llmc_alloc_device_or_managed": (I, [POINTER(c_void_p), ctypes.c_size_t, I, POINTER(c_int)]),
         "llmc_free_device_or_managed": (I, [P]),
         "llmc_gemm": (I, [P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, P, I, S]),

@@ -7,6 +7,7 @@ Two shared objects are produced next to this file (under ``lib/``):
   raw device pointers and a CUDA stream, so Python reaches them through ctypes and no PyTorch
   headers are needed at build time (a full rebuild takes seconds, cross-compiles without a GPU).
 * ``libllmc_host.so``  the C++ host runtime (data loader, RNG, tokenizer, schedulers, checkpoint IO ...).
+* ``libllmc_b200_debug.so``  (``build(debug=True)`` / ``python -m llmc_b200.build --debug``) the kernels with their debug checks on.
 
 A content hash of the sources is stored beside each library; ``build()`` is a no-op when it matches,
 so a tree whose libraries were built elsewhere is used as is.
@@ -93,6 +94,19 @@ def build_cuda(verbose=False):
     return _build_lib("libllmc_b200.so", srcs, hdrs, [nvcc], [nvcc, "-shared", "-Xcompiler", "-fPIC"], NVCC_FLAGS, verbose)
 
 
+def build_cuda_debug(verbose=False):
+    """The same kernels with -DLLMC_DEBUG_CHECKS: every 16-byte access checks its alignment and the embedding / classifier
+    kernels check their ids; a failed check is recorded in the status word and the access is skipped or clamped (the role that
+    compute-sanitizer runs play for the reference).  Relocatable device code, so that all files share one status pointer.
+    Selected at run time with LLMC_DEBUG_CHECKS=1."""
+    nvcc = _nvcc()
+    srcs = _sources("", (".cu",))
+    hdrs = _sources("", (".cuh", ".h"))
+    flags = NVCC_FLAGS + ["-rdc=true", "-DLLMC_DEBUG_CHECKS=1"]
+    return _build_lib("libllmc_b200_debug.so", srcs, hdrs, [nvcc], [nvcc, "-shared", "-rdc=true", "-gencode", "arch=compute_100a,code=sm_100a",
+                                                                    "-Xcompiler", "-fPIC"], flags, verbose)
+
+
 def build_host(verbose=False):
     cxx = os.environ.get("CXX") or shutil.which("g++") or "g++"
     srcs = _sources("host", (".cpp",))
@@ -100,9 +114,12 @@ def build_host(verbose=False):
     return _build_lib("libllmc_host.so", srcs, hdrs, [cxx], [cxx, "-shared", "-pthread"], CXX_FLAGS, verbose)
 
 
-def build(verbose=False):
-    return build_cuda(verbose), build_host(verbose)
+def build(verbose=False, debug=False):
+    out = (build_cuda(verbose), build_host(verbose))
+    if debug:
+        out += (build_cuda_debug(verbose),)
+    return out
 
 
 if __name__ == "__main__":
-    build(verbose="-q" not in sys.argv)
+    build(verbose="-q" not in sys.argv, debug="--debug" in sys.argv)

@@ -22,7 +22,8 @@ classifier_kernel(bf16* __restrict__ logits, float* __restrict__ losses, const i
     // rows are processed back to front so that the rows the LM-head GEMM wrote last (still in L2) go first
     const int row = gridDim.x - 1 - blockIdx.x;
     bf16* x = logits + (size_t)row * Vp;
-    const int target = targets[row];
+    if (threadIdx.x == 0) (void)LLMC_DBG_CHECK(targets[row] >= 0 && targets[row] < V, 0xC01);   // debug build: reported
+    const int target = min(max(targets[row], 0), V - 1);       // ids are validated on the host; never index outside the row
     const int vpack = V >> 3;                 // full packs of valid columns
     // pass 1: running maximum and sum of 2^((x - max) * log2 e), per thread, one pack at a time
     float m = -INFINITY, s = 0.f;

@@ -31,9 +31,26 @@ enum : unsigned int {
     ST_MBAR_TIMEOUT = 1,   // a wait on a shared-memory mbarrier ran out
     ST_FLAG_TIMEOUT = 2,   // a wait on a global/peer flag ran out
     ST_BAD_ARG = 3,        // a kernel-side argument check failed
+    ST_DEBUG_CHECK = 4,    // a check of the debug build failed (misaligned 16-byte access, id out of range); the access was skipped
 };
 extern "C" unsigned int* llmc_status_ptr();   // device pointer to the status word
 extern "C" int llmc_device_sm_count();
+
+// ----------------------------------------------------------------------------
+// Checks of the debug build (-DLLMC_DEBUG_CHECKS, libllmc_b200_debug.so): a failed check records ST_DEBUG_CHECK with a
+// location code in the status word and the kernel skips or clamps the access instead of faulting, so the context stays
+// usable and the host sees which check fired.  In the normal build the macro is the constant true and costs nothing.
+#ifdef LLMC_DEBUG_CHECKS
+extern __device__ unsigned int* g_llmc_dbg_status;     // defined in runtime.cu (relocatable device code in the debug build)
+__device__ __forceinline__ bool llmc_dbg_fail(unsigned int where) {
+    if (g_llmc_dbg_status) atomicCAS(g_llmc_dbg_status, 0u, (4u << 24) | (where & 0xFFFFFFu));
+    return false;
+}
+#define LLMC_DBG_CHECK(cond, where) ((cond) ? true : llmc_dbg_fail(where))
+#else
+#define LLMC_DBG_CHECK(cond, where) (true)
+#endif
+#define LLMC_ALIGNED16(p) ((reinterpret_cast<uintptr_t>(p) & 15u) == 0)
 
 // ----------------------------------------------------------------------------
 // 128-bit packs
@@ -55,18 +72,25 @@ typedef Pack128<bf16> bf16x8;
 typedef Pack128<float> f32x4;
 
 template <typename T> DEVINL Pack128<T> ld128(const T* p) {
-    Pack128<T> r; *reinterpret_cast<int4*>(&r) = *reinterpret_cast<const int4*>(p); return r;
+    Pack128<T> r;
+    if (!LLMC_DBG_CHECK(LLMC_ALIGNED16(p), 0xA10)) return Pack128<T>::zeros();
+    *reinterpret_cast<int4*>(&r) = *reinterpret_cast<const int4*>(p); return r;
 }
 template <typename T> DEVINL Pack128<T> ld128cs(const T* p) {   // streaming: do not keep in L1
-    Pack128<T> r; *reinterpret_cast<int4*>(&r) = __ldcs(reinterpret_cast<const int4*>(p)); return r;
+    Pack128<T> r;
+    if (!LLMC_DBG_CHECK(LLMC_ALIGNED16(p), 0xA11)) return Pack128<T>::zeros();
+    *reinterpret_cast<int4*>(&r) = __ldcs(reinterpret_cast<const int4*>(p)); return r;
 }
 template <typename T> DEVINL void st128(T* p, const Pack128<T>& v) {
+    if (!LLMC_DBG_CHECK(LLMC_ALIGNED16(p), 0xA20)) return;
     *reinterpret_cast<int4*>(p) = *reinterpret_cast<const int4*>(&v);
 }
 template <typename T> DEVINL void st128cs(T* p, const Pack128<T>& v) {
+    if (!LLMC_DBG_CHECK(LLMC_ALIGNED16(p), 0xA21)) return;
     __stcs(reinterpret_cast<int4*>(p), *reinterpret_cast<const int4*>(&v));
 }
 template <typename T> DEVINL void st128cg(T* p, const Pack128<T>& v) {
+    if (!LLMC_DBG_CHECK(LLMC_ALIGNED16(p), 0xA22)) return;
     __stcg(reinterpret_cast<int4*>(p), *reinterpret_cast<const int4*>(&v));
 }
 

@@ -21,6 +21,7 @@ __global__ void encoder_fwd_kernel(bf16* __restrict__ out, const int* __restrict
     const int p = (int)(idx % cp);
     const long long bt = idx / cp;
     const int t = (int)(bt % T);
+    (void)LLMC_DBG_CHECK(tokens[bt] >= 0 && tokens[bt] < V, 0xE01);     // debug build: an id outside the table is reported
     const int tok = min(max(tokens[bt], 0), V - 1);      // ids are validated on the host; never index outside the table
     bf16x8 a = ld128(wte + (size_t)tok * C + p * 8);
     if (wpe == nullptr) {                                // models with rotary positions have no position table

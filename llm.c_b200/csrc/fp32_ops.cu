@@ -67,6 +67,7 @@ __global__ void encoder_fwd_f32(float* __restrict__ out, const int* __restrict__
     const int p = (int)(idx % cp);
     const long long bt = idx / cp;
     const int t = (int)(bt % T);
+    (void)LLMC_DBG_CHECK(tokens[bt] >= 0 && tokens[bt] < V, 0xE01);     // debug build: an id outside the table is reported
     const int tok = min(max(tokens[bt], 0), V - 1);
     f32x4 o = ld128(wte + (size_t)tok * C + p * 4);
     if (wpe != nullptr) {
@@ -382,6 +383,7 @@ classifier_f32(float* __restrict__ logits, float* __restrict__ losses, const int
                int V, int Vp, int write_dlogits, int accumulate_loss) {
     __shared__ float red[32];
     float* x = logits + (size_t)blockIdx.x * Vp;
+    if (threadIdx.x == 0) (void)LLMC_DBG_CHECK(targets[blockIdx.x] >= 0 && targets[blockIdx.x] < V, 0xC01);
     const int target = min(max(targets[blockIdx.x], 0), V - 1);
     float mx = -INFINITY;
     for (int i = threadIdx.x; i < V; i += blockDim.x) mx = fmaxf(mx, x[i]);

@@ -11,6 +11,13 @@
 #include <string>
 #include <string.h>
 
+#ifdef LLMC_DEBUG_CHECKS
+__device__ unsigned int* g_llmc_dbg_status = nullptr;      // where the checks of the debug build report (this device's status word)
+extern "C" int llmc_debug_checks_enabled() { return 1; }
+#else
+extern "C" int llmc_debug_checks_enabled() { return 0; }
+#endif
+
 static unsigned int* g_status_dev[64] = {nullptr};
 static std::mutex g_mu;
 
@@ -23,6 +30,9 @@ extern "C" unsigned int* llmc_status_ptr() {
         unsigned int* p = nullptr;
         if (cudaMalloc(&p, 256) != cudaSuccess) return nullptr;
         cudaMemset(p, 0, 256);
+#ifdef LLMC_DEBUG_CHECKS
+        if (cudaMemcpyToSymbol(g_llmc_dbg_status, &p, sizeof(p)) != cudaSuccess) return nullptr;
+#endif
         g_status_dev[dev] = p;
     }
     return g_status_dev[dev];
