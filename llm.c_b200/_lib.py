@@ -78,7 +78,8 @@ def cuda():
         "llmc_swiglu_bwd": (I, [P, P, P, L, I, S]),
         "llmc_rope_cache": (I, [P, P, P, P, P, I, I, I, I, I, I, I, I, P, S]),
         "llmc_skinny_gemm": (I, [P, P, P, I, I, I, I, I, I, S]),
-        "llmc_cached_attention": (I, [P, P, P, P, I, I, I, I, I, I, I, P, S]),
+        "llmc_cached_attention": (I, [P, P, P, P, I, I, I, I, I, I, I, P, P, S]),
+        "llmc_cached_attention_workspace": (L, [I, I, I, I, I, I]),
         "llmc_gelu_bwd_inplace": (I, [P, P, L, S]),
         "llmc_residual_add": (I, [P, P, P, L, S]),
         "llmc_bias_grad_scratch": (L, [I, I]),

@@ -322,11 +322,17 @@ def rope_cache(q, kcache, vcache, raw, freqs, Tq, start_pos, NH, NKV, pos=None):
 def cached_attention(out, q, kcache, vcache, Tq, start_pos, NH, NKV, pos=None):
     """out (N, NH, HS): causal attention of the Tq new queries per batch row over cache positions 0 .. start_pos + t."""
     global _launches
+    lib = _lib.cuda()
     N = q.shape[0]
     HS = kcache.shape[-1]
-    _launches += 1
-    check(_lib.cuda().llmc_cached_attention(_p(out), _p(q), _p(kcache), _p(vcache), N // Tq, Tq, kcache.shape[1], start_pos, NH, NKV,
-                                            HS, _p(pos), _stream()), "llmc_cached_attention")
+    B, Tmax = N // Tq, kcache.shape[1]
+    # decoding steps (few query rows per cached head, head width 64 or 128) take the split-key kernel and its workspace; the
+    # buffer is kept per device, so a step captured in a CUDA graph replays on the same addresses
+    words = lib.llmc_cached_attention_workspace(B, Tq, Tmax, NH, NKV, HS)
+    ws = _scratch.get("cached_attention", words, torch.float32, q.device) if words > 0 else None
+    _launches += 2 if words > 0 else 1
+    check(lib.llmc_cached_attention(_p(out), _p(q), _p(kcache), _p(vcache), B, Tq, Tmax, start_pos, NH, NKV, HS, _p(pos), _p(ws), _stream()),
+          "llmc_cached_attention")
 
 
 def matmul_skinny(out, inp, weight):

@@ -169,7 +169,9 @@ def test_gpu_training_reduces_loss_and_is_deterministic():
 
 
 @pytest.mark.parametrize("B,Tq,start,Tmax,NH,NKV,HS", [(2, 5, 0, 16, 4, 2, 64), (3, 1, 700, 1024, 8, 2, 128), (1, 9, 40, 64, 6, 3, 96),
-                                                       (2, 3, 5, 16, 4, 4, 64), (1, 2, 1100, 1200, 2, 1, 64)])
+                                                       (2, 3, 5, 16, 4, 4, 64), (1, 2, 1100, 1200, 2, 1, 64),
+                                                       # the split-key decoding kernel: 8, 1 and 2 query rows per cached head, many slices
+                                                       (2, 2, 300, 1024, 8, 2, 128), (2, 1, 50, 512, 4, 4, 64), (1, 1, 1900, 2048, 4, 2, 64)])
 def test_decoding_kernels(B, Tq, start, Tmax, NH, NKV, HS):
     """Rotary embedding into the cache and attention over the cache against the fp32 restatement (also beyond one 512-key
     chunk of the running softmax)."""
