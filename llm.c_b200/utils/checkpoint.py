@@ -14,8 +14,8 @@ LLaMA-3 models use the reference's own header and tensor order (train_llama3.py:
   three float fields to integers; this writer also stores them exactly, as three float64 in header[17:23] (marker 1 in
   header[16]), and the padded vocabulary in header[23]; the reference's readers ignore those slots.
 
-Device tensors are streamed through a bounded pinned staging buffer, so writing a checkpoint needs no host copy of
-the whole model.
+Device tensors are streamed through two pinned staging buffers (transfer and file IO overlap), so writing or reading a
+checkpoint needs no host copy of the whole model.
 """
 import os
 import re
@@ -55,27 +55,85 @@ class _atomic_write:
         return False
 
 
-def _stream_out(f, t):
-    """Writes a (device or host) tensor to an open file in bounded chunks."""
+_staging = {}
+
+
+def _pinned_pair(dtype):
+    """Two pinned host buffers of CHUNK_ELEMS elements per element type, allocated once (reference: the double buffer of
+    device_to_file / file_to_device in llmc/cuda_common.h)."""
+    if dtype not in _staging:
+        _staging[dtype] = [torch.empty(CHUNK_ELEMS, dtype=dtype).pin_memory() for _ in range(2)]
+    return _staging[dtype]
+
+
+def _raw_view(t):
     flat = t.reshape(-1)
-    if flat.dtype == torch.bfloat16:
-        flat = flat.view(torch.int16)
-    for i in range(0, flat.numel(), CHUNK_ELEMS):
-        f.write(flat[i:i + CHUNK_ELEMS].cpu().numpy().tobytes())
+    return flat.view(torch.int16) if flat.dtype == torch.bfloat16 else flat
+
+
+def _stream_out(f, t):
+    """Writes a tensor to an open file.  Host tensors go out through their buffer, without a copy.  Device tensors are staged
+    through two pinned buffers: while chunk i is written to the file, the copy of chunk i + 1 is already running on a side
+    stream, so the device-to-host transfer and the file write overlap and no host copy of the whole tensor ever exists."""
+    view = _raw_view(t)
+    n_total = view.numel()
+    if n_total == 0:
+        return
+    if not view.is_cuda:
+        f.write(memoryview(view.contiguous().numpy()).cast("B"))
+        return
+    bufs = _pinned_pair(view.dtype)
+    side = torch.cuda.Stream(device=view.device)
+    side.wait_stream(torch.cuda.current_stream(view.device))       # whatever produced the tensor has finished
+    events = [torch.cuda.Event(), torch.cuda.Event()]
+
+    def start(chunk):
+        i = chunk * CHUNK_ELEMS
+        n = min(CHUNK_ELEMS, n_total - i)
+        with torch.cuda.stream(side):
+            bufs[chunk & 1][:n].copy_(view[i:i + n], non_blocking=True)
+            events[chunk & 1].record(side)
+        return n
+
+    chunks = (n_total + CHUNK_ELEMS - 1) // CHUNK_ELEMS
+    pending = start(0)
+    for c in range(chunks):
+        n = pending
+        if c + 1 < chunks:
+            pending = start(c + 1)            # the other buffer: its previous contents were written in the last trip
+        events[c & 1].synchronize()
+        f.write(memoryview(bufs[c & 1][:n].numpy()).cast("B"))
 
 
 def _stream_in(f, t):
-    """Fills a tensor from an open file in bounded chunks."""
-    flat = t.reshape(-1)
-    view = flat.view(torch.int16) if flat.dtype == torch.bfloat16 else flat
-    np_dtype = {torch.int16: np.int16, torch.float32: np.float32, torch.int32: np.int32}[view.dtype]
+    """Fills a tensor from an open file.  Device tensors: the file is read into one pinned buffer while the host-to-device copy
+    of the previous chunk runs from the other."""
+    view = _raw_view(t)
+    n_total = view.numel()
     esz = view.element_size()
-    for i in range(0, view.numel(), CHUNK_ELEMS):
-        n = min(CHUNK_ELEMS, view.numel() - i)
-        raw = f.read(n * esz)
-        if len(raw) != n * esz:
+    if not t.is_contiguous():
+        raise ValueError("checkpoint tensors must be contiguous")
+    if not view.is_cuda:
+        got = f.readinto(memoryview(view.numpy()).cast("B")) if n_total else 0
+        if got != n_total * esz:
             raise IOError("checkpoint file is truncated")
-        view[i:i + n].copy_(torch.from_numpy(np.frombuffer(raw, dtype=np_dtype).copy()))
+        return
+    bufs = _pinned_pair(view.dtype)
+    events = [None, None]
+    stream = torch.cuda.current_stream(view.device)
+    for c, i in enumerate(range(0, n_total, CHUNK_ELEMS)):
+        n = min(CHUNK_ELEMS, n_total - i)
+        if events[c & 1] is not None:
+            events[c & 1].synchronize()       # the copy that last read this buffer has finished
+        got = f.readinto(memoryview(bufs[c & 1][:n].numpy()).cast("B"))
+        if got != n * esz:
+            raise IOError("checkpoint file is truncated")
+        view[i:i + n].copy_(bufs[c & 1][:n], non_blocking=True)
+        events[c & 1] = torch.cuda.Event()
+        events[c & 1].record(stream)
+    for e in events:
+        if e is not None:
+            e.synchronize()                   # the staging buffers are shared: leave them idle
 
 
 def write_model(path, model):
