@@ -88,3 +88,24 @@ def test_dataset_entry_points_and_eval_summary(tmp_path, capsys):
     assert vislog.main([str(log), "--out", str(tmp_path / "c.png")]) == 0
     out = capsys.readouterr().out
     assert "trl" in out and "eval" in out
+
+
+def test_loss_parity_helpers(tmp_path):
+    """The comparison tool's parsing and bookkeeping (the runs themselves need a GPU and the reference binary)."""
+    import os
+    import sys
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline"))
+    import loss_parity as lp
+    text = "step    1/10 | loss 10.978783 (+nanz)| norm 1.2 (+nanz)| lr 8.57e-07 | 944.66 ms | 19.2% bf16 MFU | 555001 tok/s\n" \
+           "val loss 10.9\nstep    2/10 | loss 10.500000 (+0.10z)| norm 1.1\n"
+    assert lp.losses_from(text) == {1: 10.978783, 2: 10.5}
+    for name in ("DONE_00000005", "DONE_00000010", "model_00000010.bin", "state_00000010_00000.bin"):
+        (tmp_path / name).write_bytes(b"x")
+    lp.forget_later_checkpoints(str(tmp_path), 5)
+    assert sorted(os.listdir(tmp_path)) == ["DONE_00000005", "model_00000010.bin", "state_00000010_00000.bin"]
+    out = io.StringIO()
+    worst = lp.compare("t", {6: 1.0, 7: 2.0}, {6: 1.01, 7: 1.98}, range(6, 8), 0.05, out)
+    assert abs(worst - 0.02) < 1e-9 and "largest difference" in out.getvalue()
+    assert lp.compare("t", {6: 1.0}, {}, range(6, 7), 0.05, io.StringIO()) == float("inf")
+    a = lp.parse(["--cross-load", "--checkpoint-step", "3", "--model", "d6"])
+    assert a.cross_load and a.checkpoint_step == 3 and a.model == "d6"
