@@ -66,6 +66,8 @@ constexpr int IDS_PER_CTA = 64;
 constexpr int LIST_CAP = 4096;
 constexpr int WTE_THREADS = 256;
 constexpr int WTE_MAXP = 8;     // channel packs per lane per pass => 2048 channels per pass
+constexpr int WTE_SCAN = 4;     // sub-blocks of WTE_THREADS positions per scan round
+static_assert(WTE_SCAN * (WTE_THREADS / 32) == 32, "the scan of the hit counts is one warp wide");
 
 // dwte[v, :] (+)= sum over positions i (ascending) with tokens[i] == v of dout[i, :]
 __global__ void __launch_bounds__(WTE_THREADS)
@@ -73,7 +75,8 @@ wte_bwd_kernel(bf16* __restrict__ dwte, const bf16* __restrict__ dout, const int
                int N, int C, int V, int accumulate, unsigned int seed) {
     __shared__ int list_pos[LIST_CAP];
     __shared__ unsigned char list_id[LIST_CAP];
-    __shared__ int warp_counts[WTE_THREADS / 32];
+    __shared__ int warp_counts[WTE_SCAN * (WTE_THREADS / 32)];
+    __shared__ int warp_base[WTE_SCAN * (WTE_THREADS / 32)];
     __shared__ int list_len;
     __shared__ int touched[IDS_PER_CTA];     // has this id already been written in this launch (multi-round case)
 
@@ -87,26 +90,47 @@ wte_bwd_kernel(bf16* __restrict__ dwte, const bf16* __restrict__ dout, const int
 
     int pos0 = 0;
     while (pos0 < N) {
-        // ---- scan: append matching positions in position order until the list is full ----
+        // ---- scan: append matching positions in position order until the list is full.  A round covers WTE_SCAN sub-blocks of
+        //      256 positions with ONE set of barriers: per (sub-block, warp) hit counts, an exclusive scan of the 32 counts by
+        //      warp 0, then every hit is written at its final slot.  (One sub-block per round spent most of the kernel in its
+        //      three barriers per 256 tokens.)
         while (pos0 < N) {
-            if (list_len + WTE_THREADS > LIST_CAP) break;      // uniform: list_len is read after a barrier
-            const int i = pos0 + threadIdx.x;
-            int tok = (i < N) ? tokens[i] : -1;
-            const bool hit = (tok >= v0) && (tok < v0 + IDS_PER_CTA);
-            const unsigned ballot = __ballot_sync(0xffffffffu, hit);
-            if (lane == 0) warp_counts[warp] = __popc(ballot);
-            __syncthreads();
-            int base = list_len;
-            for (int w = 0; w < warp; w++) base += warp_counts[w];
-            if (hit) {
-                const int slot = base + __popc(ballot & ((1u << lane) - 1u));
-                list_pos[slot] = i;
-                list_id[slot] = (unsigned char)(tok - v0);
+            if (list_len + WTE_SCAN * WTE_THREADS > LIST_CAP) break;      // uniform: list_len is read after a barrier
+            int tok[WTE_SCAN];
+            unsigned ballot[WTE_SCAN];
+            #pragma unroll
+            for (int k = 0; k < WTE_SCAN; k++) {
+                const int i = pos0 + k * WTE_THREADS + threadIdx.x;
+                tok[k] = (i < N) ? tokens[i] : -1;
+                const bool hit = (tok[k] >= v0) && (tok[k] < v0 + IDS_PER_CTA);
+                ballot[k] = __ballot_sync(0xffffffffu, hit);
+                if (lane == 0) warp_counts[k * nwarps + warp] = __popc(ballot[k]);
             }
             __syncthreads();
-            if (threadIdx.x == 0) { int tot = 0; for (int w = 0; w < nwarps; w++) tot += warp_counts[w]; list_len += tot; }
+            if (warp == 0) {                                   // WTE_SCAN * nwarps == 32 counts, in position order
+                const int base0 = list_len;
+                const int c = warp_counts[lane];
+                int incl = c;
+                #pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int t = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (lane >= o) incl += t;
+                }
+                warp_base[lane] = base0 + incl - c;
+                __syncwarp();
+                if (lane == 31) list_len = base0 + incl;
+            }
             __syncthreads();
-            pos0 += WTE_THREADS;
+            #pragma unroll
+            for (int k = 0; k < WTE_SCAN; k++) {
+                if ((ballot[k] >> lane) & 1u) {
+                    const int slot = warp_base[k * nwarps + warp] + __popc(ballot[k] & ((1u << lane) - 1u));
+                    list_pos[slot] = pos0 + k * WTE_THREADS + threadIdx.x;
+                    list_id[slot] = (unsigned char)(tok[k] - v0);
+                }
+            }
+            __syncthreads();                                   // the list is complete; the count tables may be rewritten
+            pos0 += WTE_SCAN * WTE_THREADS;
         }
         const int len = list_len;
         // ---- reduce: warp w handles ids w, w + nwarps, ... ----
