@@ -109,3 +109,12 @@ def test_loss_parity_helpers(tmp_path):
     assert lp.compare("t", {6: 1.0}, {}, range(6, 7), 0.05, io.StringIO()) == float("inf")
     a = lp.parse(["--cross-load", "--checkpoint-step", "3", "--model", "d6"])
     assert a.cross_load and a.checkpoint_step == 3 and a.model == "d6"
+
+
+def test_both_kernel_libraries_build_and_identify_themselves():
+    """The normal and the debug build of the kernel library compile for sm_100a without a GPU, and each says which one it is."""
+    import ctypes
+    from llmc_b200 import build
+    normal, dbg = build.build_cuda(), build.build_cuda_debug()
+    assert ctypes.CDLL(normal).llmc_debug_checks_enabled() == 0
+    assert ctypes.CDLL(dbg).llmc_debug_checks_enabled() == 1
