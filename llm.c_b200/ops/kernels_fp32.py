@@ -13,7 +13,7 @@ from .. import _lib
 from .._lib import check
 from . import kernels
 from .kernels import _p, _scratch, _stream
-from .reference import matmul_dgrad, matmul_forward, matmul_wgrad, _view_slices     # noqa: F401  (re-exported: same path as before)
+from .reference import matmul_dgrad, matmul_forward, matmul_wgrad     # noqa: F401  (re-exported: the matmuls of this mode, see above)
 
 F32 = torch.float32
 
