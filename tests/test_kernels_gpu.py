@@ -83,7 +83,9 @@ def test_matmul_dgrad_dgelu():
 
 
 @pytest.mark.parametrize("M,OC,C,acc", [(256, 128, 256, False), (4096, 768, 768, True), (2048, 2304, 768, True),
-                                          (1000, 264, 136, True), (8192, 256, 512, False)])
+                                          (1000, 264, 136, True), (8192, 256, 512, False),
+                                          # two-SM kernel, three K splits, partial tiles in both directions (fold kernel bounds)
+                                          (4096, 1600, 1600, True), (2048, 1336, 1544, False)])
 def test_matmul_wgrad(M, OC, C, acc):
     dout, inp = rnd(M, OC, scale=0.1), rnd(M, C)
     dw0 = rnd(OC, C)
